@@ -35,7 +35,7 @@ from typing import Mapping, Sequence
 import numpy as np
 import torch
 
-from simply_b200.cache.needs import PagedKVNeed, SlotStateNeed
+from simply_b200.cache.needs import PagedKVNeed, SlotStateNeed, flatten_needs
 from simply_b200.cache.page_pool import OutOfPages, PagePool
 
 
@@ -110,7 +110,8 @@ class PagedCache:
   name: str
   group: int  # index into CacheManager.groups
   need: PagedKVNeed
-  # [num_pages, 2 (keys, values), num_kv_heads, page_size, head_dim]
+  # [num_pages, 2 (keys, values), num_kv_heads, page_size, head_dim]; `need.storage_shape` where
+  # keys and values differ in size or the cache holds one entry per several tokens
   storage: torch.Tensor | None
 
 
@@ -157,8 +158,13 @@ class CacheManager:
     self.groups: list[PageGroup] = []
     self.paged: dict[str, PagedCache] = {}
     self.states: dict[str, SlotState] = {}
+    # Caches of mixers that asked with a dictionary of needs: name -> {key: handle} (nested alike).
+    self.bundles: dict[str, dict] = {}
     group_of_key: dict[tuple, int] = {}
+    single: list[tuple[str, object]] = []
     for name, need in needs.items():
+      single += flatten_needs(name, need)
+    for name, need in single:
       if need is None:
         continue
       if isinstance(need, PagedKVNeed):
@@ -181,8 +187,8 @@ class CacheManager:
         storage = None
         if device is not None:
           storage = torch.zeros(
-              (self.groups[g].num_pages, 2, need.num_kv_heads, page_size, need.head_dim),
-              dtype=dtype, device=device)
+              need.storage_shape(self.groups[g].num_pages, page_size),
+              dtype=getattr(torch, need.dtype) if need.dtype else dtype, device=device)
         self.paged[name] = PagedCache(name, g, need, storage)
       elif isinstance(need, SlotStateNeed):
         storage = None
@@ -192,6 +198,16 @@ class CacheManager:
         self.states[name] = SlotState(name, need, storage)
       else:
         raise TypeError(f"cache {name!r}: unknown kind of need {need!r}")
+    handles = {**self.paged, **self.states}
+
+    def bundle(name: str, need):
+      if isinstance(need, dict):
+        return {key: bundle(f"{name}.{key}", sub) for key, sub in need.items()}
+      return handles.get(name)
+
+    for name, need in needs.items():
+      if isinstance(need, dict):
+        self.bundles[name] = bundle(name, need)
     self.lengths = np.zeros(max_slots, dtype=np.int64)
     # Per slot, what the usual decode step asks in one look: up to which length a step may bring
     # tokens without taking a page (the smallest group's held pages), and from which length on

@@ -2,7 +2,8 @@
 
 A mixer with a growing cache asks for paged keys and values (`PagedKVNeed`); a
 mixer with state of fixed size asks for a per-request slot (`SlotStateNeed`); a
-mixer without memory asks for nothing.  The reference's counterpart of the first
+mixer without memory asks for nothing; a mixer that needs several of these asks
+with a dictionary and gets a dictionary of handles.  The reference's counterpart of the first
 is `DecodeStateConfig` (simply/utils/ragged_paged_attention.py:113-173); it has no
 counterpart of the second (its per-request rows hold tokens and positions only,
 :1451-1461).
@@ -33,6 +34,28 @@ class PagedKVNeed:
   num_kv_heads: int
   head_dim: int
   window: int | None = None
+  # Size of a value head where it differs from a key head's (None: the same).
+  value_dim: int | None = None
+  # One entry per `stride` tokens instead of one per token (a cache of block summaries): the entry
+  # of the tokens b*stride .. b*stride + stride - 1 lives in the page of token b*stride.
+  stride: int = 1
+  # Storage type where it is not the activations' ("float32").
+  dtype: str | None = None
+
+  @property
+  def v_dim(self) -> int:
+    return self.head_dim if self.value_dim is None else self.value_dim
+
+  def entries_per_page(self, page_size: int) -> int:
+    return -(-page_size // self.stride)
+
+  def storage_shape(self, num_pages: int, page_size: int) -> tuple[int, ...]:
+    """Per page all key rows `[num_kv_heads, entries, head_dim]`, then all value rows
+    `[num_kv_heads, entries, v_dim]`; with equal sizes that is `[2, heads, entries, head_dim]`."""
+    entries = self.entries_per_page(page_size)
+    if self.v_dim == self.head_dim:
+      return (num_pages, 2, self.num_kv_heads, entries, self.head_dim)
+    return (num_pages, self.num_kv_heads * entries * (self.head_dim + self.v_dim))
 
   def group_key(self) -> tuple:
     """Needs with equal keys share page ids: the same pages are held, and given back together."""
@@ -86,3 +109,14 @@ class SlotStateNeed:
 
   shape: tuple[int, ...]
   dtype: str = "float32"
+
+
+def flatten_needs(name: str, need) -> list[tuple[str, object]]:
+  """A mixer may ask for several caches at once as a dictionary `{key: need}` (nested ones too: a
+  mixer made of mixers).  Returns `[(name.key..., need)]` for every single need inside."""
+  if isinstance(need, dict):
+    out = []
+    for key, sub in need.items():
+      out += flatten_needs(f"{name}.{key}", sub)
+    return out
+  return [(name, need)]

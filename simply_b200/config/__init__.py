@@ -8,6 +8,7 @@ from typing import Any
 
 from simply_b200.config.engine_config import EngineConfig
 from simply_b200.config.gemma2 import ConfigError, Gemma2Config
+from simply_b200.config.generax import GeneraxConfig
 from simply_b200.config.model_spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from simply_b200.registry import ARCHITECTURES
 
@@ -25,6 +26,8 @@ def read_config_json(model_dir: str) -> dict[str, Any]:
 def config_from_dict(d: dict[str, Any]):
   """Picks the config class by config.json's `architectures[0]` and builds it."""
   archs = d.get("architectures")
+  if not archs and isinstance(d.get("architecture"), str):
+    archs = [d["architecture"]]  # some designs name theirs with one string
   if not archs:
     raise ConfigError("config.json has no 'architectures' entry")
   try:
@@ -56,7 +59,7 @@ def preset(name: str):
 
 
 __all__ = [
-    "ConfigError", "EngineConfig", "Gemma2Config", "LayerCall", "LayerSpec", "ModelSpec",
+    "ConfigError", "EngineConfig", "Gemma2Config", "GeneraxConfig", "LayerCall", "LayerSpec", "ModelSpec",
     "PartSpec", "config_from_dict", "load_config", "preset", "preset_dict", "preset_names",
     "read_config_json",
 ]

@@ -10,6 +10,13 @@
 //   p = softmax(s) in float32, o = p . v          simply/model_lib.py:633-637
 //   query head n reads kv head n / (Hq / Hkv)     simply/model_lib.py:2306-2310
 //
+// Options beyond that (`sb_paged_attention_general`): value heads of another size than key heads
+// (a page then holds all its key rows, then all its value rows), and pooled blocks: with a
+// window W and blocks of P tokens, position i also sees, ahead of its window and under the same
+// softmax, one key and value per block c with c*P + P - 1 <= i - W, read from a second paged
+// storage (float32) that holds one entry per P tokens in the page of the block's first token.
+// Blocks are visited in tiles of 32 by block number, before the tokens.
+//
 // This is the true 32-bit path's attention and the fallback of the bfloat16
 // path for shapes its tensor-core kernels refuse.
 #include <float.h>
@@ -40,14 +47,59 @@ template <> struct Vec16<bf16> {
   }
 };
 
+// One tile of up to 32 keys, one per lane: scores, the running softmax, and the values' sum.
+// `kr` / `vr` are this lane's key and value rows (null where the lane has no key).
+template <typename KT>
+__device__ __forceinline__ void gen_tile(const KT* kr, const KT* vr, const float* qs, int head_dim, int v_dim,
+                                         float cap, int lane, float& m_run, float& l_run, float* acc) {
+  constexpr int VN = Vec16<KT>::N;
+  const float NEG = -0.5f * FLT_MAX;  // the reference's mask value, simply/utils/common.py:543-551
+  const bool valid = kr != nullptr;
+  float s = NEG;
+  if (valid) {
+    float dot = 0.f;
+    int d = 0;
+    if ((head_dim % VN) == 0) {
+      for (; d < head_dim; d += VN) {
+        float kf[VN];
+        Vec16<KT>::load(kr + d, kf);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) dot = fmaf(qs[d + e], kf[e], dot);
+      }
+    } else {
+      for (; d < head_dim; ++d) dot = fmaf(qs[d], to_f32<KT>(kr[d]), dot);
+    }
+    s = cap > 0.f ? cap * tanhf(dot / cap) : dot;
+  }
+  const float m_new = fmaxf(m_run, warp_max(s));
+  const float alpha = expf(m_run - m_new);
+  const float p = valid ? expf(s - m_new) : 0.f;
+  l_run = l_run * alpha + warp_sum(p);
+  m_run = m_new;
+#pragma unroll
+  for (int i = 0; i < GEN_MAX_DPL; ++i) acc[i] *= alpha;
+  const unsigned valid_mask = __ballot_sync(0xffffffffu, valid);
+  for (int jj = 0; jj < 32; ++jj) {
+    if (!((valid_mask >> jj) & 1u)) continue;  // uniform over the warp
+    const float pj = __shfl_sync(0xffffffffu, p, jj);
+    const KT* vj = reinterpret_cast<const KT*>(__shfl_sync(0xffffffffu, (unsigned long long)vr, jj));
+#pragma unroll
+    for (int i = 0; i < GEN_MAX_DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < v_dim) acc[i] = fmaf(pj, to_f32<KT>(vj[d]), acc[i]);
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(GEN_WARPS * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ cache,
                                const int* __restrict__ block_table, int max_pages,
                                const int* __restrict__ token_seq, const int* __restrict__ positions,
                                T* __restrict__ out, int num_tokens, int num_q_heads, int num_kv_heads,
-                               int head_dim, int page_size, int num_pages, float cap, int window,
-                               int* err) {
+                               int head_dim, int v_dim, int page_size, int num_pages, float cap, int window,
+                               const float* __restrict__ pool, const int* __restrict__ pool_table,
+                               int pool_max_pages, int pool_len, int pool_pages, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
   extern __shared__ float smem[];  // per warp: head_dim floats of q
@@ -63,81 +115,71 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
   __syncwarp();
 
   const int lo = window > 0 ? max(pos - window + 1, 0) : 0;
-  const float NEG = -0.5f * FLT_MAX;  // the reference's mask value, simply/utils/common.py:543-551
-  float m_run = NEG, l_run = 0.f;
+  float m_run = -0.5f * FLT_MAX, l_run = 0.f;
   float acc[GEN_MAX_DPL];
 #pragma unroll
   for (int i = 0; i < GEN_MAX_DPL; ++i) acc[i] = 0.f;
-  const size_t head_stride = (size_t)page_size * head_dim;
-  const size_t kv_stride = (size_t)num_kv_heads * head_stride;
-  constexpr int VN = Vec16<T>::N;
 
-  for (int tile = (lo / 32) * 32; tile <= pos; tile += 32) {
-    const int j = tile + lane;
-    bool valid = j >= lo && j <= pos;
-    long long page = -1;
-    if (valid) {
-      page = block_table[(size_t)b * max_pages + j / page_size];
-      if (page < 0 || page >= num_pages) {
-        atomicOr(err, SB_ERR_BAD_PAGE);
-        valid = false;
-      }
-    }
-    const int off = j % page_size;
-    float s = NEG;
-    if (valid) {
-      const T* kr = cache + ((size_t)page * 2) * kv_stride + m * head_stride + (size_t)off * head_dim;
-      float dot = 0.f;
-      int d = 0;
-      if ((head_dim % VN) == 0) {
-        for (; d < head_dim; d += VN) {
-          float kf[VN];
-          Vec16<T>::load(kr + d, kf);
-#pragma unroll
-          for (int e = 0; e < VN; ++e) dot = fmaf(qs[d + e], kf[e], dot);
+  if (pool != nullptr && window > 0 && pool_len > 0) {
+    // Blocks that lie wholly before the window: c * P + P - 1 <= pos - window.
+    const int num_blocks = pos - window + 1 > 0 ? (pos - window + 1) / pool_len : 0;
+    const int entries = (page_size + pool_len - 1) / pool_len;
+    const size_t page_stride = (size_t)num_kv_heads * entries * (head_dim + v_dim);
+    for (int tile = 0; tile < num_blocks; tile += 32) {
+      const int c = tile + lane;
+      const float* kr = nullptr;
+      const float* vr = nullptr;
+      if (c < num_blocks) {
+        const long long start = (long long)c * pool_len;
+        const long long page = pool_table[(size_t)b * pool_max_pages + start / page_size];
+        if (page < 0 || page >= pool_pages) {
+          atomicOr(err, SB_ERR_BAD_PAGE);
+        } else {
+          const size_t row = (size_t)m * entries + (start % page_size) / pool_len;
+          kr = pool + page * page_stride + row * head_dim;
+          vr = pool + page * page_stride + (size_t)num_kv_heads * entries * head_dim + row * v_dim;
         }
-      } else {
-        for (; d < head_dim; ++d) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
       }
-      s = cap > 0.f ? cap * tanhf(dot / cap) : dot;
-    }
-    const float m_new = fmaxf(m_run, warp_max(s));
-    const float alpha = expf(m_run - m_new);
-    const float p = valid ? expf(s - m_new) : 0.f;
-    l_run = l_run * alpha + warp_sum(p);
-    m_run = m_new;
-#pragma unroll
-    for (int i = 0; i < GEN_MAX_DPL; ++i) acc[i] *= alpha;
-    const unsigned valid_mask = __ballot_sync(0xffffffffu, valid);
-    for (int jj = 0; jj < 32; ++jj) {
-      if (!((valid_mask >> jj) & 1u)) continue;  // uniform over the warp
-      const float pj = __shfl_sync(0xffffffffu, p, jj);
-      const long long pgj = __shfl_sync(0xffffffffu, page, jj);
-      const int offj = (tile + jj) % page_size;
-      const T* vr = cache + ((size_t)pgj * 2 + 1) * kv_stride + m * head_stride + (size_t)offj * head_dim;
-#pragma unroll
-      for (int i = 0; i < GEN_MAX_DPL; ++i) {
-        const int d = lane + 32 * i;
-        if (d < head_dim) acc[i] = fmaf(pj, to_f32<T>(vr[d]), acc[i]);
-      }
+      gen_tile<float>(kr, vr, qs, head_dim, v_dim, cap, lane, m_run, l_run, acc);
     }
   }
-  T* op = out + ((size_t)t * num_q_heads + n) * head_dim;
+
+  const size_t page_stride = (size_t)num_kv_heads * page_size * (head_dim + v_dim);
+  const size_t value_base = (size_t)num_kv_heads * page_size * head_dim;
+  for (int tile = (lo / 32) * 32; tile <= pos; tile += 32) {
+    const int j = tile + lane;
+    const T* kr = nullptr;
+    const T* vr = nullptr;
+    if (j >= lo && j <= pos) {
+      const long long page = block_table[(size_t)b * max_pages + j / page_size];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(err, SB_ERR_BAD_PAGE);
+      } else {
+        const size_t row = (size_t)m * page_size + j % page_size;
+        kr = cache + page * page_stride + row * head_dim;
+        vr = cache + page * page_stride + value_base + row * v_dim;
+      }
+    }
+    gen_tile<T>(kr, vr, qs, head_dim, v_dim, cap, lane, m_run, l_run, acc);
+  }
+  T* op = out + ((size_t)t * num_q_heads + n) * v_dim;
   const float inv = 1.0f / l_run;
 #pragma unroll
   for (int i = 0; i < GEN_MAX_DPL; ++i) {
     const int d = lane + 32 * i;
-    if (d < head_dim) op[d] = from_f32<T>(acc[i] * inv);
+    if (d < v_dim) op[d] = from_f32<T>(acc[i] * inv);
   }
 }
 
-extern "C" int sb_paged_attention_generic(const void* q, int dtype, const void* cache, const int* block_table,
+extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* cache, const int* block_table,
                                           int max_pages, const int* token_seq, const int* positions,
                                           void* out, int num_tokens, int num_q_heads, int num_kv_heads,
-                                          int head_dim, int page_size, int num_pages, float cap, int window,
-                                          int* err, cudaStream_t stream) {
+                                          int head_dim, int v_dim, int page_size, int num_pages, float cap,
+                                          int window, const float* pool, const int* pool_table,
+                                          int pool_max_pages, int pool_len, int pool_pages, int* err,
+                                          cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  if (head_dim <= 0 || head_dim > 32 * GEN_MAX_DPL) return -7;
+  if (head_dim <= 0 || head_dim > 32 * GEN_MAX_DPL || v_dim <= 0 || v_dim > 32 * GEN_MAX_DPL) return -7;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return -8;
   const long long items = (long long)num_tokens * num_q_heads;
   const unsigned blocks = (unsigned)((items + GEN_WARPS - 1) / GEN_WARPS);
@@ -145,11 +187,23 @@ extern "C" int sb_paged_attention_generic(const void* q, int dtype, const void* 
   if (dtype == SB_DTYPE_F32)
     sb_launch(paged_attention_generic_kernel<float>, blocks, GEN_WARPS * 32, smem, stream, (const float*)q,
         (const float*)cache, block_table, max_pages, token_seq, positions, (float*)out, num_tokens,
-        num_q_heads, num_kv_heads, head_dim, page_size, num_pages, cap, window, err);
+        num_q_heads, num_kv_heads, head_dim, v_dim, page_size, num_pages, cap, window, pool, pool_table,
+        pool_max_pages, pool_len, pool_pages, err);
   else
     sb_launch(paged_attention_generic_kernel<bf16>, blocks, GEN_WARPS * 32, smem, stream, (const bf16*)q,
         (const bf16*)cache, block_table, max_pages, token_seq, positions, (bf16*)out, num_tokens,
-        num_q_heads, num_kv_heads, head_dim, page_size, num_pages, cap, window, err);
+        num_q_heads, num_kv_heads, head_dim, v_dim, page_size, num_pages, cap, window, pool, pool_table,
+        pool_max_pages, pool_len, pool_pages, err);
   SB_LAUNCH_CHECK();
   return 0;
+}
+
+extern "C" int sb_paged_attention_generic(const void* q, int dtype, const void* cache, const int* block_table,
+                                          int max_pages, const int* token_seq, const int* positions,
+                                          void* out, int num_tokens, int num_q_heads, int num_kv_heads,
+                                          int head_dim, int page_size, int num_pages, float cap, int window,
+                                          int* err, cudaStream_t stream) {
+  return sb_paged_attention_general(q, dtype, cache, block_table, max_pages, token_seq, positions, out, num_tokens,
+                                    num_q_heads, num_kv_heads, head_dim, head_dim, page_size, num_pages, cap,
+                                    window, nullptr, nullptr, 0, 0, 0, err, stream);
 }

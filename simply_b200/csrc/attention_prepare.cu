@@ -1,0 +1,227 @@
+// What stands around attention with normed queries and keys: the norm over whole projections,
+// rotations of keys, queries and values, the stores into the paged cache, the pooled blocks'
+// means, and the turn back of a head's result.  Float32 arithmetic; T is the storage type.
+//
+//   x     = x / sqrt(mean_row x^2 + eps) * w                 over all heads of q (of k) at once
+//   (a, b)= (a cos - b sin, b cos + a sin)                   pair (i, i + n/2), angle = pos * freq[i]
+//   q    *= head_scale[head]
+// A page of the cache holds all its key rows [kv head, entry, head_dim], then all its value
+// rows [kv head, entry, value_dim].
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// One block per token.  qkv row: q (H d) | k (G d) | v (G dv); G = 0: a layer without keys and
+// values of its own.  rot_freq [rot_dims / 2] (null: no rotation), value_freq [dv / 2] (null:
+// values are stored as they are).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_rotate_store_kernel(const T* __restrict__ qkv, int row_width, const float* __restrict__ q_norm,
+                            const float* __restrict__ k_norm, float eps, const float* __restrict__ head_scale,
+                            const float* __restrict__ rot_freq, int rot_dims, const float* __restrict__ value_freq,
+                            T* __restrict__ q_out, T* __restrict__ cache, const int* __restrict__ block_table,
+                            int max_pages, const int* __restrict__ token_seq, const int* __restrict__ positions,
+                            int H, int G, int d, int dv, int page_size, int num_pages, int write_cache, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ float row[];  // (H + G) d floats + 33 scratch
+  const int nq = H * d, nk = G * d;
+  float* scratch = row + nq + nk;
+  const int t = blockIdx.x;
+  const T* x = qkv + (size_t)t * row_width;
+  const float pos = (float)positions[t];
+
+  float ssq = 0.f, ssk = 0.f;
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+    const float v = to_f32<T>(x[i]);
+    row[i] = v;
+    if (i < nq) ssq = fmaf(v, v, ssq); else ssk = fmaf(v, v, ssk);
+  }
+  ssq = block_sum(ssq, scratch);
+  const float rq = 1.0f / sqrtf(ssq / (float)nq + eps);
+  float rk = 0.f;
+  if (nk > 0) {
+    ssk = block_sum(ssk, scratch);
+    rk = 1.0f / sqrtf(ssk / (float)nk + eps);
+  }
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x)
+    row[i] = i < nq ? row[i] * rq * q_norm[i] : row[i] * rk * k_norm[i - nq];
+  __syncthreads();
+
+  long long page = -1;
+  int off = 0;
+  if (write_cache && nk > 0) {
+    const int p = positions[t];
+    page = block_table[(size_t)token_seq[t] * max_pages + p / page_size];
+    off = p % page_size;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_PAGE);
+      page = -1;
+    }
+  }
+  const size_t page_stride = (size_t)G * page_size * (d + dv);
+  const int half = rot_dims / 2;
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+    const int head = i / d, c = i % d;
+    float v = row[i];
+    if (rot_freq != nullptr && c < rot_dims) {
+      const int pair = c < half ? c : c - half;
+      float sn, cs;
+      sincosf(pos * rot_freq[pair], &sn, &cs);
+      const float a = row[i - c + pair], b = row[i - c + pair + half];
+      v = c < half ? a * cs - b * sn : b * cs + a * sn;
+    }
+    if (i < nq) {
+      q_out[(size_t)t * nq + i] = from_f32<T>(v * head_scale[head]);
+    } else if (page >= 0) {
+      const int m = head - H;
+      cache[page * page_stride + ((size_t)m * page_size + off) * d + c] = from_f32<T>(v);
+    }
+  }
+  if (page >= 0) {
+    const T* vx = x + nq + nk;
+    T* dst = cache + page * page_stride + (size_t)G * page_size * d;
+    const int vhalf = dv / 2;
+    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+      const int m = i / dv, c = i % dv;
+      float v = to_f32<T>(vx[i]);
+      if (value_freq != nullptr) {
+        const int pair = c < vhalf ? c : c - vhalf;
+        float sn, cs;
+        sincosf(pos * value_freq[pair], &sn, &cs);
+        const float a = to_f32<T>(vx[i - c + pair]), b = to_f32<T>(vx[i - c + pair + vhalf]);
+        v = c < vhalf ? a * cs - b * sn : b * cs + a * sn;
+      }
+      dst[((size_t)m * page_size + off) * dv + c] = from_f32<T>(v);
+    }
+  }
+}
+
+extern "C" int sb_qk_norm_rotate_store(const void* qkv, int row_width, int dtype, const float* q_norm,
+                                       const float* k_norm, float eps, const float* head_scale,
+                                       const float* rot_freq, int rot_dims, const float* value_freq, void* q_out,
+                                       void* cache, const int* block_table, int max_pages, const int* token_seq,
+                                       const int* positions, int num_tokens, int H, int G, int d, int dv,
+                                       int page_size, int num_pages, int write_cache, int* err,
+                                       cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const size_t smem = ((size_t)(H + G) * d + 33) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  if (rot_dims % 2 || rot_dims > d || (value_freq != nullptr && dv % 2)) return -4;
+  if (dtype == SB_DTYPE_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(qk_norm_rotate_store_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb_launch(qk_norm_rotate_store_kernel<float>, num_tokens, 256, smem, stream, (const float*)qkv, row_width,
+              q_norm, k_norm, eps, head_scale, rot_freq, rot_dims, value_freq, (float*)q_out, (float*)cache,
+              block_table, max_pages, token_seq, positions, H, G, d, dv, page_size, num_pages, write_cache, err);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(qk_norm_rotate_store_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb_launch(qk_norm_rotate_store_kernel<bf16>, num_tokens, 256, smem, stream, (const bf16*)qkv, row_width,
+              q_norm, k_norm, eps, head_scale, rot_freq, rot_dims, value_freq, (bf16*)q_out, (bf16*)cache,
+              block_table, max_pages, token_seq, positions, H, G, d, dv, page_size, num_pages, write_cache, err);
+  }
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Pooled blocks: for every block of P tokens whose last token arrived in this step, the mean of
+// its keys and of its values as the cache holds them, summed in the tokens' order, into the
+// float32 storage of block entries.  Grid (block within the step, sequence, kv head).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+pool_blocks_kernel(const T* __restrict__ cache, const int* __restrict__ block_table, int max_pages, int num_pages,
+                   float* __restrict__ pool, const int* __restrict__ pool_table, int pool_max_pages,
+                   int pool_pages, const int* __restrict__ cu_q, const int* __restrict__ q_start, int G, int d,
+                   int dv, int page_size, int P, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int b = blockIdx.y, m = blockIdx.z;
+  const int start = q_start[b], end = start + cu_q[b + 1] - cu_q[b];
+  const int c = start / P + blockIdx.x;
+  if (c >= end / P) return;
+  const long long first = (long long)c * P;
+  const int entries = (page_size + P - 1) / P;
+  const long long to = pool_table[(size_t)b * pool_max_pages + first / page_size];
+  if (to < 0 || to >= pool_pages) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_PAGE);
+    return;
+  }
+  const size_t page_stride = (size_t)G * page_size * (d + dv);
+  const size_t pool_stride = (size_t)G * entries * (d + dv);
+  const size_t entry = (size_t)m * entries + (first % page_size) / P;
+  for (int ch = threadIdx.x; ch < d + dv; ch += blockDim.x) {
+    const bool is_key = ch < d;
+    const int cc = is_key ? ch : ch - d;
+    const int width = is_key ? d : dv;
+    const size_t base = is_key ? 0 : (size_t)G * page_size * d;
+    float sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < P; ++j) {
+      const long long p = first + j;
+      const long long page = block_table[(size_t)b * max_pages + p / page_size];
+      if (page < 0 || page >= num_pages) { ok = false; break; }
+      sum += to_f32<T>(cache[page * page_stride + base + ((size_t)m * page_size + p % page_size) * width + cc]);
+    }
+    if (!ok) {
+      atomicOr(err, SB_ERR_BAD_PAGE);
+      continue;
+    }
+    float* dst = pool + to * pool_stride + (is_key ? 0 : (size_t)G * entries * d) + entry * width + cc;
+    *dst = sum / (float)P;
+  }
+}
+
+extern "C" int sb_pool_blocks(const void* cache, int dtype, const int* block_table, int max_pages, int num_pages,
+                              float* pool, const int* pool_table, int pool_max_pages, int pool_pages,
+                              const int* cu_q, const int* q_start, int num_seqs, int max_blocks, int G, int d,
+                              int dv, int page_size, int P, int* err, cudaStream_t stream) {
+  if (num_seqs == 0 || max_blocks <= 0) return 0;
+  if (P <= 0) return -13;
+  const dim3 grid(max_blocks, num_seqs, G);
+  if (dtype == SB_DTYPE_F32)
+    sb_launch(pool_blocks_kernel<float>, grid, 128, 0, stream, (const float*)cache, block_table, max_pages,
+              num_pages, pool, pool_table, pool_max_pages, pool_pages, cu_q, q_start, G, d, dv, page_size, P, err);
+  else
+    sb_launch(pool_blocks_kernel<bf16>, grid, 128, 0, stream, (const bf16*)cache, block_table, max_pages,
+              num_pages, pool, pool_table, pool_max_pages, pool_pages, cu_q, q_start, G, d, dv, page_size, P, err);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Turns every head of x [T, H, n] by its token's position: pair (i, i + n/2) by
+// sign * pos * freq[i].  One block per token.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotate_heads_kernel(const T* __restrict__ x, const int* __restrict__ positions, const float* __restrict__ freq,
+                    float sign, int H, int n, T* __restrict__ out) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, half = n / 2;
+  const float pos = sign * (float)positions[t];
+  for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+    const int h = i / half, pair = i % half;
+    const size_t at = ((size_t)t * H + h) * n + pair;
+    float sn, cs;
+    sincosf(pos * freq[pair], &sn, &cs);
+    const float a = to_f32<T>(x[at]), b = to_f32<T>(x[at + half]);
+    out[at] = from_f32<T>(a * cs - b * sn);
+    out[at + half] = from_f32<T>(b * cs + a * sn);
+  }
+}
+
+extern "C" int sb_rotate_heads(const void* x, int dtype, const int* positions, const float* freq, float sign,
+                               int num_tokens, int H, int n, void* out, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (n % 2) return -4;
+  if (dtype == SB_DTYPE_F32)
+    sb_launch(rotate_heads_kernel<float>, num_tokens, 256, 0, stream, (const float*)x, positions, freq, sign, H, n,
+              (float*)out);
+  else
+    sb_launch(rotate_heads_kernel<bf16>, num_tokens, 256, 0, stream, (const bf16*)x, positions, freq, sign, H, n,
+              (bf16*)out);
+  SB_LAUNCH_CHECK();
+  return 0;
+}

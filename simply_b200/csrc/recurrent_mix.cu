@@ -1,0 +1,352 @@
+// Kernels of the recurrent mixers: the gated delta rule with its short convolutions, and the
+// mean of RMS-normed branches.  Everything here computes in float32; T is the storage type of
+// the activations that come in from and go out to matrix products.
+//
+//   inputs    y_c[t] = silu(sum_j w[c, j] x_c[t - (taps-1) + j])   x before the request's start is
+//                                                                   0, before the step's start it
+//                                                                   comes from the request's state
+//             q, k   = y / sqrt(sum_head y^2 + 1e-6)   (q also times head_dim^-1/2)
+//             beta   = sigmoid(b),  g = exp(-exp(A) * softplus(a + dt))
+//   scan      S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//   output    o / sqrt(mean_head o^2 + eps) * w * sigmoid(gate)
+//   mean      (1/n) sum_i x_i / sqrt(mean x_i^2 + eps) * w_i
+#include "common.cuh"
+
+#define SB_ERR_BAD_SLOT 16  // a state slot outside the state tensor
+
+__device__ __forceinline__ float sigmoid_f32(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ---------------------------------------------------------------------------
+// Inputs of the delta rule.  One block per token.
+//   pre  [T, pre_width]: q | k | v | b   (q, k: G heads of d; v: H heads of dv; b: H)
+//   low  [T, low_width]: a (H * d) | ...
+//   conv_state [slots, taps - 1, C] float32, C = 2 G d + H dv
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_inputs_kernel(const T* __restrict__ pre, int pre_width, const T* __restrict__ low, int low_width,
+                    const float* __restrict__ conv_w, const float* __restrict__ conv_state,
+                    const float* __restrict__ dt_bias, const float* __restrict__ neg_rate,
+                    const int* __restrict__ token_seq, const int* __restrict__ cu_q, const int* __restrict__ slots,
+                    int num_slots, int taps, int G, int H, int d, int dv,
+                    float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out,
+                    float* __restrict__ decay_out, float* __restrict__ beta_out, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ float y[];  // C floats
+  const int t = blockIdx.x;
+  const int b = token_seq[t];
+  const int first = cu_q[b];
+  const int i = t - first;
+  int slot = slots[b];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
+    slot = 0;
+  }
+  const int qk = G * d, C = 2 * qk + H * dv;
+  const float* state = conv_state + (size_t)slot * (taps - 1) * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int idx = i - (taps - 1) + j;
+      const float x = idx >= 0 ? to_f32<T>(pre[(size_t)(first + idx) * pre_width + c])
+                               : state[(size_t)(taps - 1 + idx) * C + c];
+      acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+    }
+    y[c] = acc * sigmoid_f32(acc);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const float q_scale = 1.0f / sqrtf((float)d);
+  for (int head = warp; head < 2 * G; head += nwarps) {  // q heads, then k heads
+    const float* src = y + (size_t)head * d;
+    float ss = 0.f;
+    for (int c = lane; c < d; c += 32) ss = fmaf(src[c], src[c], ss);
+    ss = warp_sum(ss);
+    float scale = 1.0f / sqrtf(ss + 1e-6f);
+    float* dst;
+    if (head < G) {
+      scale *= q_scale;
+      dst = q_out + ((size_t)t * G + head) * d;
+    } else {
+      dst = k_out + ((size_t)t * G + (head - G)) * d;
+    }
+    for (int c = lane; c < d; c += 32) dst[c] = src[c] * scale;
+  }
+  for (int c = threadIdx.x; c < H * dv; c += blockDim.x) v_out[(size_t)t * H * dv + c] = y[2 * qk + c];
+  for (int h = threadIdx.x; h < H; h += blockDim.x)
+    beta_out[(size_t)t * H + h] = sigmoid_f32(to_f32<T>(pre[(size_t)t * pre_width + C + h]));
+  for (int c = threadIdx.x; c < H * d; c += blockDim.x) {
+    const float a = to_f32<T>(low[(size_t)t * low_width + c]) + dt_bias[c];
+    decay_out[(size_t)t * H * d + c] = expf(neg_rate[c / d] * softplus_f32(a));
+  }
+}
+
+// The convolution's state after the step: the last taps - 1 inputs of (state, new inputs).  One
+// thread per (sequence, channel), ascending, so that it reads only what it has not yet written.
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ pre, int pre_width, float* __restrict__ conv_state,
+                                  const int* __restrict__ cu_q, const int* __restrict__ slots, int num_slots,
+                                  int taps, int C) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int b = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int slot = slots[b];
+  if (c >= C || slot < 0 || slot >= num_slots) return;
+  const int first = cu_q[b], n = cu_q[b + 1] - first;
+  float* state = conv_state + (size_t)slot * (taps - 1) * C;
+  for (int r = 0; r < taps - 1; ++r) {
+    const int idx = n - (taps - 1) + r;
+    state[(size_t)r * C + c] = idx >= 0 ? to_f32<T>(pre[(size_t)(first + idx) * pre_width + c])
+                                        : state[(size_t)(taps - 1 + idx) * C + c];
+  }
+}
+
+extern "C" int sb_delta_inputs(const void* pre, int pre_width, const void* low, int low_width, int dtype,
+                               const float* conv_w, float* conv_state, const float* dt_bias,
+                               const float* neg_rate, const int* token_seq, const int* cu_q, const int* slots,
+                               int num_tokens, int num_seqs, int num_slots, int taps, int G, int H, int d, int dv,
+                               float* q_out, float* k_out, float* v_out, float* decay_out, float* beta_out,
+                               int* err, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const int C = 2 * G * d + H * dv;
+  const size_t smem = (size_t)C * sizeof(float);
+  if (taps < 1 || G <= 0 || H % G || smem > 200 * 1024) return -13;
+  if (dtype == SB_DTYPE_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_inputs_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb_launch(delta_inputs_kernel<float>, num_tokens, 256, smem, stream, (const float*)pre, pre_width,
+              (const float*)low, low_width, conv_w, (const float*)conv_state, dt_bias, neg_rate, token_seq, cu_q,
+              slots, num_slots, taps, G, H, d, dv, q_out, k_out, v_out, decay_out, beta_out, err);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_inputs_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb_launch(delta_inputs_kernel<bf16>, num_tokens, 256, smem, stream, (const bf16*)pre, pre_width,
+              (const bf16*)low, low_width, conv_w, (const float*)conv_state, dt_bias, neg_rate, token_seq, cu_q,
+              slots, num_slots, taps, G, H, d, dv, q_out, k_out, v_out, decay_out, beta_out, err);
+  }
+  SB_LAUNCH_CHECK();
+  if (taps > 1) {
+    const dim3 grid((C + 127) / 128, num_seqs);
+    if (dtype == SB_DTYPE_F32)
+      sb_launch(conv_state_kernel<float>, grid, 128, 0, stream, (const float*)pre, pre_width, conv_state, cu_q,
+                slots, num_slots, taps, C);
+    else
+      sb_launch(conv_state_kernel<bf16>, grid, 128, 0, stream, (const bf16*)pre, pre_width, conv_state, cu_q,
+                slots, num_slots, taps, C);
+    SB_LAUNCH_CHECK();
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// The scan.  A block owns `cols` value columns of one (sequence, head) and walks the sequence's
+// tokens of this step in order.  A column of S is held by RS neighbouring lanes, each with the
+// rows rs, rs + RS, ... (at most 32) in registers; the two sums over rows per token are
+// butterfly sums over those lanes, in an order that does not depend on the step's shape.  k, q,
+// g, v and beta of SCAN_CHUNK tokens at a time are staged in shared memory.
+// ---------------------------------------------------------------------------
+#define SCAN_CHUNK 8
+#define SCAN_ROWS 32
+
+template <int RS>
+__global__ void __launch_bounds__(128)
+delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                  const float* __restrict__ decay, const float* __restrict__ beta, float* __restrict__ state,
+                  const int* __restrict__ cu_q, const int* __restrict__ slots, int num_slots, int G, int H, int d,
+                  int dv, int cols, float* __restrict__ out, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ float stage[];  // SCAN_CHUNK * (3 d + cols + 1)
+  const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
+  const int rs = threadIdx.x % RS, col_local = threadIdx.x / RS;
+  const int col = col0 + col_local;
+  const bool on = col_local < cols && col < dv;
+  const int first = cu_q[b], n = cu_q[b + 1] - first;
+  const int slot = slots[b];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
+    return;
+  }
+  const int g_head = h / (H / G);
+  float* S = state + ((size_t)slot * H + h) * d * dv;
+  float s[SCAN_ROWS];
+#pragma unroll
+  for (int r = 0; r < SCAN_ROWS; ++r) {
+    const int row = rs + RS * r;
+    s[r] = (on && row < d) ? S[(size_t)row * dv + col] : 0.f;
+  }
+  const int per_token = 3 * d + cols + 1;
+  for (int base = 0; base < n; base += SCAN_CHUNK) {
+    const int count = min(SCAN_CHUNK, n - base);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < count * per_token; idx += blockDim.x) {
+      const int i = idx / per_token, e = idx % per_token;
+      const size_t t = (size_t)(first + base + i);
+      float x;
+      if (e < d) x = k[(t * G + g_head) * d + e];
+      else if (e < 2 * d) x = q[(t * G + g_head) * d + (e - d)];
+      else if (e < 3 * d) x = decay[(t * H + h) * d + (e - 2 * d)];
+      else if (e < 3 * d + cols) x = (col0 + e - 3 * d) < dv ? v[(t * H + h) * dv + col0 + (e - 3 * d)] : 0.f;
+      else x = beta[t * H + h];
+      stage[idx] = x;
+    }
+    __syncthreads();
+    for (int i = 0; i < count; ++i) {
+      const float* kk = stage + i * per_token;
+      const float* qq = kk + d;
+      const float* gg = kk + 2 * d;
+      const float vv = kk[3 * d + min(col_local, cols - 1)];
+      const float bb = kk[3 * d + cols];
+      float dot = 0.f;
+#pragma unroll
+      for (int r = 0; r < SCAN_ROWS; ++r) {
+        const int row = rs + RS * r;
+        if (row < d) {
+          s[r] *= gg[row];
+          dot = fmaf(s[r], kk[row], dot);
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = bb * (vv - dot);
+      float od = 0.f;
+#pragma unroll
+      for (int r = 0; r < SCAN_ROWS; ++r) {
+        const int row = rs + RS * r;
+        if (row < d) {
+          s[r] = fmaf(kk[row], u, s[r]);
+          od = fmaf(s[r], qq[row], od);
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < RS; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
+      if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = od;
+    }
+  }
+  if (on) {
+#pragma unroll
+    for (int r = 0; r < SCAN_ROWS; ++r) {
+      const int row = rs + RS * r;
+      if (row < d) S[(size_t)row * dv + col] = s[r];
+    }
+  }
+}
+
+extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, const float* decay, const float* beta,
+                             float* state, const int* cu_q, const int* slots, int num_seqs, int num_slots, int G,
+                             int H, int d, int dv, float* out, int* err, cudaStream_t stream) {
+  if (num_seqs == 0) return 0;
+  if (d <= 0 || d > 32 * SCAN_ROWS || dv <= 0 || G <= 0 || H % G) return -13;
+  int rs = 1;
+  while (rs * SCAN_ROWS < d) rs <<= 1;
+  const int threads = 128;
+  int cols = threads / rs;
+  if (cols > dv) cols = dv;
+  // Few (sequence, head) pairs: narrower blocks, so that more SMs share the columns.
+  while (cols > 8 && (long long)num_seqs * H * ((dv + cols - 1) / cols) < 296) cols = (cols + 1) / 2;
+  const int block = ((cols * rs + 31) / 32) * 32;
+  const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
+  const size_t smem = (size_t)SCAN_CHUNK * (3 * d + cols + 1) * sizeof(float);
+#define SB_SCAN(RS_)                                                                                          \
+  sb_launch(delta_scan_kernel<RS_>, grid, block, smem, stream, q, k, v, decay, beta, state, cu_q, slots,     \
+            num_slots, G, H, d, dv, cols, out, err)
+  switch (rs) {
+    case 1: SB_SCAN(1); break;
+    case 2: SB_SCAN(2); break;
+    case 4: SB_SCAN(4); break;
+    case 8: SB_SCAN(8); break;
+    case 16: SB_SCAN(16); break;
+    default: SB_SCAN(32); break;
+  }
+#undef SB_SCAN
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Output of the delta rule: per head RMS norm, channel scale, gate.  One block per token, a warp
+// per head.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ low, int low_width, int gate_offset,
+                       const float* __restrict__ w, float eps, int H, int dv, T* __restrict__ out) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < H; h += nwarps) {
+    const float* src = o + ((size_t)t * H + h) * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(src[c], src[c], ss);
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)dv + eps);
+    for (int c = lane; c < dv; c += 32) {
+      const float gate = sigmoid_f32(to_f32<T>(low[(size_t)t * low_width + gate_offset + h * dv + c]));
+      out[((size_t)t * H + h) * dv + c] = from_f32<T>(src[c] * rstd * w[c] * gate);
+    }
+  }
+}
+
+extern "C" int sb_gated_head_norm(const float* o, const void* low, int low_width, int gate_offset, int dtype,
+                                  const float* w, float eps, int num_tokens, int H, int dv, void* out,
+                                  cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (dtype == SB_DTYPE_F32)
+    sb_launch(gated_head_norm_kernel<float>, num_tokens, 256, 0, stream, o, (const float*)low, low_width,
+              gate_offset, w, eps, H, dv, (float*)out);
+  else
+    sb_launch(gated_head_norm_kernel<bf16>, num_tokens, 256, 0, stream, o, (const bf16*)low, low_width,
+              gate_offset, w, eps, H, dv, (bf16*)out);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Mean of up to four RMS-normed branches.  One block per token.
+// ---------------------------------------------------------------------------
+struct MeanBranches {
+  const void* x[4];
+  const float* w[4];
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+normed_mean_kernel(MeanBranches br, int count, float eps, int width, T* __restrict__ out) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  float rstd[4];
+  for (int i = 0; i < count; ++i) {
+    const T* x = reinterpret_cast<const T*>(br.x[i]) + (size_t)t * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float a = to_f32<T>(x[c]);
+      ss = fmaf(a, a, ss);
+    }
+    ss = block_sum(ss, scratch);
+    rstd[i] = 1.0f / sqrtf(ss / (float)width + eps);
+  }
+  const float share = 1.0f / (float)count;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < count; ++i)
+      acc += to_f32<T>(reinterpret_cast<const T*>(br.x[i])[(size_t)t * width + c]) * rstd[i] * br.w[i][c];
+    out[(size_t)t * width + c] = from_f32<T>(acc * share);
+  }
+}
+
+extern "C" int sb_normed_mean(const void* x0, const void* x1, const void* x2, const void* x3, const float* w0,
+                              const float* w1, const float* w2, const float* w3, int count, int dtype, float eps,
+                              int num_tokens, int width, void* out, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (count < 1 || count > 4) return -13;
+  MeanBranches br = {{x0, x1, x2, x3}, {w0, w1, w2, w3}};
+  if (dtype == SB_DTYPE_F32)
+    sb_launch(normed_mean_kernel<float>, num_tokens, 256, 0, stream, br, count, eps, width, (float*)out);
+  else
+    sb_launch(normed_mean_kernel<bf16>, num_tokens, 256, 0, stream, br, count, eps, width, (bf16*)out);
+  SB_LAUNCH_CHECK();
+  return 0;
+}

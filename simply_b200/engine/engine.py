@@ -88,7 +88,7 @@ class Engine:
         step_tokens=None if ec.max_window_cache_tokens < 0 else ec.max_num_issue_tokens,
         burst_tokens=min(max(ec.intermediate_steps, 1), 64),
         windowed_cache_tokens=max(ec.max_window_cache_tokens, 0))
-    self.caches = {**self.cache.paged, **self.cache.states}
+    self.caches = {**self.cache.paged, **self.cache.states, **self.cache.bundles}
     eos = getattr(config, "eos_token_id", None)
     eos_ids = () if eos is None else (tuple(eos) if isinstance(eos, (tuple, list)) else (eos,))
     self.scheduler = Scheduler(self.cache, max_num_issue_tokens=ec.max_num_issue_tokens,

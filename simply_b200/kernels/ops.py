@@ -30,6 +30,7 @@ _ERRORS = {
     2: "a token id outside the embedding table",
     4: "a gather row outside the batch",
     8: "a wait for a bulk copy timed out",
+    16: "a state slot outside the state tensor",
 }
 _STATUS = {
     -2: "row too wide for the norm kernel's shared-memory buffer",
@@ -43,6 +44,7 @@ _STATUS = {
     -10: "batch outside the decode-advance kernel's range",
     -11: "head size does not allow a tensor map",
     -12: "the driver refused to encode a tensor map",
+    -13: "sizes outside the recurrent-mixer kernels' range",
 }
 
 
@@ -221,6 +223,24 @@ class CudaOps:
                                c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_int, c_void],
         "sb_paged_attention_generic": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
+        "sb_paged_attention_general": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
+                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void,
+                                       c_int, c_int, c_int, c_void, c_void],
+        "sb_qk_norm_rotate_store": [c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_int, c_void,
+                                    c_void, c_void, c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
+                                    c_int, c_int, c_int, c_void, c_void],
+        "sb_pool_blocks": [c_void, c_int, c_void, c_int, c_int, c_void, c_void, c_int, c_int, c_void, c_void, c_int,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void],
+        "sb_rotate_heads": [c_void, c_int, c_void, c_void, c_float, c_int, c_int, c_int, c_void, c_void],
+        "sb_delta_inputs": [c_void, c_int, c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void,
+                            c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void,
+                            c_void, c_void, c_void, c_void],
+        "sb_delta_scan": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_void, c_void, c_void],
+        "sb_gated_head_norm": [c_void, c_void, c_int, c_int, c_int, c_void, c_float, c_int, c_int, c_int, c_void,
+                               c_void],
+        "sb_normed_mean": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_float,
+                           c_int, c_int, c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
         "sb_sample_logprobs": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void, c_void],
         "sb_decode_advance": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void],
@@ -728,10 +748,24 @@ class CudaOps:
   # ---- attention ------------------------------------------------------------
   def paged_attention(self, q: torch.Tensor, storage: torch.Tensor, block_table: torch.Tensor, ctx: Any, *,
                       num_heads: int, num_kv_heads: int, head_dim: int, logit_softcap: float,
-                      window: int | None) -> torch.Tensor:
+                      window: int | None, value_dim: int | None = None, pooled: tuple | None = None) -> torch.Tensor:
+    """`value_dim`: size of a value head where it is not the key heads'.  `pooled`: (storage of block
+    entries, its block table, block length): with a window, one key and value per whole block that
+    has left the window, under the same softmax (csrc/attention_generic.cu)."""
     t = q.shape[0]
-    out = self._new(t, num_heads * head_dim, dtype=q.dtype)
+    value_dim = head_dim if value_dim is None else value_dim
+    out = self._new(t, num_heads * value_dim, dtype=q.dtype)
     group = num_heads // num_kv_heads
+    if pooled is not None or value_dim != head_dim:
+      pool, pool_table, pool_len = pooled if pooled is not None else (None, None, 0)
+      if pool is not None and pool.dtype != torch.float32:
+        raise KernelError("block entries are kept in float32")
+      self._call("sb_paged_attention_general", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
+                 block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
+                 num_kv_heads, head_dim, value_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
+                 int(window or 0), _ptr(pool), _ptr(pool_table), pool_table.shape[1] if pool is not None else 0,
+                 int(pool_len), pool.shape[0] if pool is not None else 0, _ptr(self.err))
+      return out
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
       prefill, decode, _, prefill_tc, prefill_pair = self._attention_lib(head_dim)
       use_tc = prefill_tc is not None and self._prefill_uses_tcgen05(head_dim, group, ctx.page_size)
@@ -776,6 +810,86 @@ class CudaOps:
                block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
                num_kv_heads, head_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
                int(window or 0), _ptr(self.err))
+    return out
+
+  # ---- attention with normed queries and keys ---------------------------------
+  def qk_norm_rotate_store(self, qkv: torch.Tensor, q_norm: torch.Tensor, k_norm: torch.Tensor | None, eps: float,
+                           head_scale: torch.Tensor, rot_freq: torch.Tensor | None, value_freq: torch.Tensor | None,
+                           num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                           storage: torch.Tensor | None, block_table: torch.Tensor, ctx: Any) -> torch.Tensor:
+    """qkv [T, q | k | v] -> queries [T, num_heads, head_dim], normed over the whole projection,
+    rotated and scaled per head; keys (normed, rotated) and values (rotated with `value_freq`) go
+    into the pages of `storage` (csrc/attention_prepare.cu).  `num_kv_heads = 0`: queries only."""
+    t = qkv.shape[0]
+    q = self._new(t, num_heads, head_dim, dtype=qkv.dtype)
+    if storage is not None and storage.dtype != qkv.dtype:
+      raise KernelError("cache and activations must share one dtype")
+    self._call("sb_qk_norm_rotate_store", _ptr(qkv), qkv.shape[1], _code(qkv), _ptr(q_norm), _ptr(k_norm), float(eps),
+               _ptr(head_scale), _ptr(rot_freq), 2 * rot_freq.numel() if rot_freq is not None else 0,
+               _ptr(value_freq), _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1],
+               _ptr(ctx.token_seq), _ptr(ctx.positions), t, num_heads, num_kv_heads, head_dim, value_dim,
+               ctx.page_size, storage.shape[0] if storage is not None else 0, int(storage is not None),
+               _ptr(self.err))
+    return q
+
+  def pool_blocks(self, storage: torch.Tensor, block_table: torch.Tensor, pool_storage: torch.Tensor,
+                  pool_table: torch.Tensor, ctx: Any, num_kv_heads: int, head_dim: int, value_dim: int,
+                  pool: int) -> None:
+    """Writes the mean key and value of every block of `pool` tokens that the step completes."""
+    self._call("sb_pool_blocks", _ptr(storage), _code(storage), _ptr(block_table), block_table.shape[1],
+               storage.shape[0], _ptr(pool_storage), _ptr(pool_table), pool_table.shape[1], pool_storage.shape[0],
+               _ptr(ctx.cu_q), _ptr(ctx.q_start), ctx.num_seqs, ctx.max_q_len // pool + 1, num_kv_heads, head_dim,
+               value_dim, ctx.page_size, pool, _ptr(self.err))
+
+  def rotate_heads(self, x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, num_heads: int, dim: int,
+                   inverse: bool = False) -> torch.Tensor:
+    out = self._new(*x.shape, dtype=x.dtype)
+    self._call("sb_rotate_heads", _ptr(x), _code(x), _ptr(positions), _ptr(freq), -1.0 if inverse else 1.0,
+               x.shape[0], num_heads, dim, _ptr(out))
+    return out
+
+  # ---- gated delta rule -------------------------------------------------------
+  def delta_rule_inputs(self, pre: torch.Tensor, low: torch.Tensor, conv_weight: torch.Tensor,
+                        conv_state: torch.Tensor, decay_bias: torch.Tensor, neg_rate: torch.Tensor, ctx: Any, *,
+                        conv_taps: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int):
+    """Convolutions with their state, activations, unit vectors, decays and beta (csrc/recurrent_mix.cu):
+    float32 q, k [T, kv heads, head_dim], v [T, heads, value_dim], decay [T, heads, head_dim], beta [T, heads]."""
+    t = pre.shape[0]
+    f32 = torch.float32
+    q = self._new(t, num_kv_heads, head_dim, dtype=f32)
+    k = self._new(t, num_kv_heads, head_dim, dtype=f32)
+    v = self._new(t, num_heads, value_dim, dtype=f32)
+    decay = self._new(t, num_heads, head_dim, dtype=f32)
+    beta = self._new(t, num_heads, dtype=f32)
+    self._call("sb_delta_inputs", _ptr(pre), pre.shape[1], _ptr(low), low.shape[1], _code(pre), _ptr(conv_weight),
+               _ptr(conv_state), _ptr(decay_bias), _ptr(neg_rate), _ptr(ctx.token_seq), _ptr(ctx.cu_q),
+               _ptr(ctx.slots), t, ctx.num_seqs, conv_state.shape[0], conv_taps, num_kv_heads, num_heads, head_dim,
+               value_dim, _ptr(q), _ptr(k), _ptr(v), _ptr(decay), _ptr(beta), _ptr(self.err))
+    self.launches += conv_taps > 1
+    return q, k, v, decay, beta
+
+  def gated_delta_scan(self, q, k, v, decay, beta, state: torch.Tensor, ctx: Any, *, num_heads: int,
+                       num_kv_heads: int, head_dim: int, value_dim: int) -> torch.Tensor:
+    """Walks every sequence's tokens through its state [slots, heads, head_dim, value_dim]; float32 o."""
+    out = self._new(q.shape[0], num_heads, value_dim, dtype=torch.float32)
+    self._call("sb_delta_scan", _ptr(q), _ptr(k), _ptr(v), _ptr(decay), _ptr(beta), _ptr(state), _ptr(ctx.cu_q),
+               _ptr(ctx.slots), ctx.num_seqs, state.shape[0], num_kv_heads, num_heads, head_dim, value_dim,
+               _ptr(out), _ptr(self.err))
+    return out
+
+  def gated_head_norm(self, o: torch.Tensor, low: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float,
+                      num_heads: int, value_dim: int) -> torch.Tensor:
+    out = self._new(o.shape[0], num_heads * value_dim, dtype=low.dtype)
+    self._call("sb_gated_head_norm", _ptr(o), _ptr(low), low.shape[1], gate_offset, _code(low), _ptr(weight),
+               float(eps), o.shape[0], num_heads, value_dim, _ptr(out))
+    return out
+
+  def normed_mean(self, branches: Sequence[torch.Tensor], scales: Sequence[torch.Tensor], eps: float) -> torch.Tensor:
+    x = [b if b.dtype == self.dtype else self.cast(b, self.dtype) for b in branches]
+    out = self._new(*x[0].shape)
+    pad = [None] * (4 - len(x))
+    self._call("sb_normed_mean", *[_ptr(b) for b in x], *pad, *[_ptr(w) for w in scales], *pad, len(x),
+               _code(out), float(eps), x[0].shape[0], x[0].shape[1], _ptr(out))
     return out
 
   # ---- sampling -------------------------------------------------------------

@@ -11,6 +11,8 @@ is read and written once per branch.
   h += post_mixer_norm(mixer(pre_mixer_norm(h)))
   h += post_ff_norm(feed_forward(pre_ff_norm(h)))
 `pre_norm` is the same without post norms (use_post_ln=False).
+`parallel_residual` has one norm whose output both sublayers read:
+  h += mixer(norm(h)) + feed_forward(norm(h))
 """
 
 from __future__ import annotations
@@ -21,6 +23,7 @@ import torch
 
 from simply_b200.config.model_spec import PartSpec
 from simply_b200.parts.base import Block, FeedForward, Mixer, Norm, build_part
+from simply_b200.parts.feedforward import NoFeedForward
 from simply_b200.parts.norm import RMSNorm
 from simply_b200.registry import BLOCKS, NORMS
 from simply_b200.weights.loader import TensorSpec
@@ -122,3 +125,43 @@ class SandwichNormBlock(Block):
 class PreNormBlock(SandwichNormBlock):
 
   uses_post_norms = False
+
+
+@BLOCKS.register("parallel_residual")
+class ParallelResidualBlock(Block):
+  """One norm; the mixer and the feed-forward (if the layer has one) both read its output, and both
+  results are added to the stream."""
+
+  def __init__(self, prefix: str, width: int, norm: PartSpec, mixer: Mixer, feed_forward: FeedForward,
+               names: dict[str, str] | None = None):
+    self.prefix = prefix
+    self.mixer = mixer
+    self.feed_forward = None if isinstance(feed_forward, NoFeedForward) else feed_forward
+    params = {"width": width, **norm.params}
+    role = (names or {}).get("norm")
+    if role is not None:
+      params["name"] = f"{prefix}.{role}"  # the scale's whole tensor name
+    self.norm = build_part(NORMS, PartSpec(norm.kind, f"{prefix}.norm", params))
+
+  def _parts(self) -> list:
+    return [p for p in (self.mixer, self.feed_forward, self.norm) if p is not None]
+
+  def cache_need(self):
+    return self.mixer.cache_need()
+
+  @property
+  def graph_safe(self) -> bool:
+    return all(p.graph_safe for p in self._parts())
+
+  def tensor_specs(self) -> list[TensorSpec]:
+    return [s for p in self._parts() for s in p.tensor_specs()]
+
+  def bind(self, tensors, ops) -> None:
+    for p in self._parts():
+      p.bind(tensors, ops)
+
+  def forward(self, stream: ResidualStream, ctx: Any, cache: Any, writes_cache: bool = True) -> None:
+    y = stream.normed(self.norm, ctx)
+    stream.add(self.mixer.forward(y, ctx, cache, writes_cache), None, ctx)
+    if self.feed_forward is not None:
+      stream.add(self.feed_forward.forward(y, ctx), None, ctx)

@@ -3,7 +3,8 @@
 `token_embedding`: rows of the table times a constant, sqrt(width) for Gemma 2
 (simply/utils/module.py:450-481).  `tied_head`: logits = x . table^T with the
 same table, no bias, then the final soft cap (simply/model_lib.py:3183-3188,
-simply/utils/module.py:416-433); logits are produced in float32.
+simply/utils/module.py:416-433); logits are produced in float32.  `linear_head`
+is the same with a table of its own.
 """
 
 from __future__ import annotations
@@ -22,8 +23,8 @@ class TokenEmbedding(Embedding):
 
   graph_safe = True
 
-  def __init__(self, prefix: str, vocab_size: int, width: int, scale: float = 1.0):
-    self.name = f"{prefix}.weight"
+  def __init__(self, prefix: str, vocab_size: int, width: int, scale: float = 1.0, name: str | None = None):
+    self.name = name or f"{prefix}.weight"
     self.vocab_size = vocab_size
     self.width = width
     self.scale = float(scale)
@@ -66,3 +67,25 @@ class TiedHead(Head):
 
   def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
     return ctx.ops.lm_head(x, self.embedding.table, self.logit_softcap)
+
+
+@HEADS.register("linear_head")
+class LinearHead(Head):
+  """An output layer with a table of its own: logits = x . W^T, then the final soft cap."""
+
+  graph_safe = True
+
+  def __init__(self, prefix: str, embedding: Embedding, logit_softcap: float = 0.0, name: str | None = None):
+    self.name = name or f"{prefix}.weight"
+    self.vocab_size, self.width = embedding.vocab_size, embedding.width
+    self.logit_softcap = float(logit_softcap or 0.0)
+    self.table: torch.Tensor | None = None
+
+  def tensor_specs(self) -> list[TensorSpec]:
+    return [TensorSpec(self.name, (self.vocab_size, self.width), "matrix")]
+
+  def bind(self, tensors, ops) -> None:
+    self.table = tensors[self.name]
+
+  def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
+    return ctx.ops.lm_head(x, self.table, self.logit_softcap)

@@ -28,14 +28,16 @@ class GatedFeedForward(FeedForward):
 
   graph_safe = True
 
-  def __init__(self, prefix: str, width: int, hidden: int, activation: str):
+  def __init__(self, prefix: str, width: int, hidden: int, activation: str,
+               names: dict[str, str] | None = None):
     self.prefix = prefix
     self.width = width
     self.hidden = hidden
     self.activation = ACTIVATIONS.get(activation)
-    self.gate_proj = Linear(f"{prefix}.gate_proj.weight", hidden, width)
-    self.up_proj = Linear(f"{prefix}.up_proj.weight", hidden, width)
-    self.down_proj = Linear(f"{prefix}.down_proj.weight", width, hidden)
+    names = names or {}  # role -> the tensor's name after the prefix
+    self.gate_proj = Linear(f"{prefix}.{names.get('gate', 'gate_proj.weight')}", hidden, width)
+    self.up_proj = Linear(f"{prefix}.{names.get('up', 'up_proj.weight')}", hidden, width)
+    self.down_proj = Linear(f"{prefix}.{names.get('down', 'down_proj.weight')}", width, hidden)
     self.gate_up_weight: torch.Tensor | None = None
 
   def tensor_specs(self) -> list[TensorSpec]:
@@ -50,3 +52,16 @@ class GatedFeedForward(FeedForward):
     ops = ctx.ops
     z = ops.gated_linear(x, self.gate_up_weight, self.activation)
     return self.down_proj(z, ctx)
+
+
+@FEED_FORWARDS.register("none")
+class NoFeedForward(FeedForward):
+  """A layer without a feed-forward: block arrangements skip it."""
+
+  graph_safe = True
+
+  def __init__(self, prefix: str = ""):
+    pass
+
+  def forward(self, x: torch.Tensor, ctx: Any) -> None:
+    return None

@@ -22,6 +22,8 @@ from simply_b200.weights.loader import TensorSpec
 
 # Importing the part modules registers the built-in parts.
 from simply_b200.parts import attention as _attention  # noqa: F401
+from simply_b200.parts import delta_rule as _delta_rule  # noqa: F401
+from simply_b200.parts import normed_attention as _normed_attention  # noqa: F401
 from simply_b200.parts import embedding as _embedding  # noqa: F401
 from simply_b200.parts import feedforward as _feedforward  # noqa: F401
 from simply_b200.parts import norm as _norm  # noqa: F401
@@ -81,8 +83,8 @@ class DecoderModel:
     for call, cache in zip(self.spec.run_order, self.cache_names):
       if not call.writes_cache:
         need, have = self.blocks[call.layer].cache_need(), needs[cache]
-        same = (type(need) is type(have)) and all(
-            getattr(need, f) == getattr(have, f) for f in ("num_kv_heads", "head_dim")
+        same = (type(need) is type(have)) and not isinstance(have, dict) and all(
+            getattr(need, f) == getattr(have, f) for f in ("num_kv_heads", "head_dim", "value_dim")
             if hasattr(have, f))
         if not same:
           raise ValueError(f"layer {call.layer!r} cannot read cache {cache!r}: {need} vs {have}")

@@ -21,15 +21,15 @@ class RMSNorm(Norm):
 
   graph_safe = True
 
-  def __init__(self, prefix: str, width: int, eps: float, plus_one: bool = True):
-    self.name = f"{prefix}.weight"
+  def __init__(self, prefix: str, width: int, eps: float, plus_one: bool = True, name: str | None = None):
+    self.name = name or f"{prefix}.weight"  # `name`: the scale's whole tensor name, where it is not "<prefix>.weight"
     self.width = width
     self.eps = float(eps)
     self.plus_one = bool(plus_one)
     self.weight: torch.Tensor | None = None
 
   def tensor_specs(self) -> list[TensorSpec]:
-    return [TensorSpec(self.name, (self.width,), "scale")]
+    return [TensorSpec(self.name, (self.width,), "scale" if self.plus_one else "gain")]
 
   def bind(self, tensors, ops) -> None:
     self.weight = tensors[self.name]

@@ -34,9 +34,13 @@ from simply_b200.weights import safetensors_io as st
 class TensorSpec:
   """A tensor the model needs.
 
+  shape: a size of -1 is one that only the file gives (a low rank that no configuration key
+    names); the part reads it off the tensor in `bind`.
   kind: "matrix" (weights of a linear map or an embedding table), "scale"
-    (a norm's per-channel scale) or "table" (integers).  The kind decides how
-    random-weights mode fills it; the loader only uses it for integer tables.
+    (a norm's per-channel scale that is applied as 1 + w, or an offset), "gain" (a
+    per-channel factor applied as it is, so that random-weights mode draws it around
+    1) or "table" (integers).  The kind decides how random-weights mode fills it; the
+    loader only uses it for integer tables.
   optional: may be absent from the files (e.g. a duplicate of a tied table).
   precision: "activation" (narrowed to the activation dtype on load), "stored" (a tensor stored
     in 32 bits stays in 32 bits) or None: "stored" for scales, "activation" otherwise.
@@ -50,7 +54,7 @@ class TensorSpec:
 
   def keeps_stored_precision(self) -> bool:
     if self.precision is None:
-      return self.kind == "scale"
+      return self.kind in ("scale", "gain")
     if self.precision not in ("activation", "stored"):
       raise ValueError(f"{self.name}: precision must be 'activation' or 'stored', got {self.precision!r}")
     return self.precision == "stored"
@@ -89,7 +93,7 @@ def check(specs: Iterable[TensorSpec], entries: dict[str, st.TensorEntry]) -> No
     e = entries.get(s.name)
     if e is None:
       continue
-    if tuple(e.shape) != tuple(s.shape):
+    if len(e.shape) != len(s.shape) or any(want not in (-1, got) for want, got in zip(s.shape, e.shape)):
       wrong_shape.append((s.name, tuple(s.shape), tuple(e.shape)))
     if (s.kind == "table") == e.is_float:
       wrong_kind.append((s.name, "integers" if s.kind == "table" else "floating point", e.dtype))

@@ -42,11 +42,15 @@ def random_tensors(
     if s.kind == "table":
       out[s.name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
       continue
-    std = scale_std if s.kind == "scale" else matrix_std
+    if any(n < 0 for n in s.shape):
+      raise ValueError(f"{s.name}: a size that only a file gives cannot be drawn at random; the configuration must name it")
+    std = scale_std if s.kind in ("scale", "gain") else matrix_std
     if std == 0.0:
       t = torch.zeros(s.shape, dtype=torch.float32, device=device)
     else:
       t = torch.randn(s.shape, generator=gen, dtype=torch.float32, device=device) * std
+    if s.kind == "gain":
+      t = t + 1.0
     out[s.name] = t.to(dtype)
   return out
 

@@ -135,7 +135,11 @@ class ReferenceOps:
 
   # ---- attention ------------------------------------------------------------
   def paged_attention(self, q, storage, block_table, ctx, *, num_heads, num_kv_heads, head_dim,
-                      logit_softcap, window):
+                      logit_softcap, window, value_dim=None, pooled=None):
+    if pooled is not None or (value_dim is not None and value_dim != head_dim):
+      assert not logit_softcap
+      return self._general_attention(q, storage, block_table, ctx, num_heads, num_kv_heads, head_dim,
+                                     value_dim or head_dim, window, pooled)
     t = q.shape[0]
     out = torch.zeros(t, num_heads, head_dim, dtype=torch.float32, device=q.device)
     group = num_heads // num_kv_heads
@@ -163,6 +167,168 @@ class ReferenceOps:
         p = torch.softmax(s, dim=-1)
         out[r0:r1, n, :] = p @ kv[:, 1, m, :]
     return out.reshape(t, num_heads * head_dim).to(self.dtype)
+
+  # ---- attention with normed queries and keys, pooled blocks ------------------
+  @staticmethod
+  def _kv_views(storage, num_kv_heads, entries, head_dim, value_dim):
+    """Keys [pages, G, entries, d] and values [pages, G, entries, dv] of a cache's storage."""
+    flat = storage.view(storage.shape[0], -1)
+    nk = num_kv_heads * entries * head_dim
+    return (flat[:, :nk].view(-1, num_kv_heads, entries, head_dim),
+            flat[:, nk:].view(-1, num_kv_heads, entries, value_dim))
+
+  @staticmethod
+  def _turn(x, angle):
+    half = x.shape[-1] // 2
+    a, b = x[..., :half], x[..., half:]
+    c, s = torch.cos(angle), torch.sin(angle)
+    return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+  def qk_norm_rotate_store(self, qkv, q_norm, k_norm, eps, head_scale, rot_freq, value_freq, num_heads,
+                           num_kv_heads, head_dim, value_dim, storage, block_table, ctx):
+    t = qkv.shape[0]
+    nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+    pos = ctx.positions.float()
+
+    def normed(x, w, heads):
+      x = x.float()
+      x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+      x = x.reshape(t, heads, head_dim)
+      if rot_freq is not None:
+        dims = 2 * rot_freq.numel()
+        angle = (pos[:, None] * rot_freq[None, :])[:, None, :]
+        x = torch.cat([self._turn(x[..., :dims], angle), x[..., dims:]], dim=-1)
+      return x
+
+    q = (normed(qkv[:, :nq], q_norm, num_heads) * head_scale.float()[None, :, None]).to(self.dtype)
+    if storage is not None and num_kv_heads:
+      k = normed(qkv[:, nq:nq + nk], k_norm, num_kv_heads)
+      v = qkv[:, nq + nk:nq + nk + num_kv_heads * value_dim].float().reshape(t, num_kv_heads, value_dim)
+      if value_freq is not None:
+        v = self._turn(v, (pos[:, None] * value_freq[None, :])[:, None, :])
+      keys, values = self._kv_views(storage, num_kv_heads, ctx.page_size, head_dim, value_dim)
+      p = ctx.positions.long()
+      page = block_table[ctx.token_seq.long(), p // ctx.page_size].long()
+      assert (page >= 0).all(), "a token would be written to a page its request does not hold"
+      keys[page, :, p % ctx.page_size, :] = k.to(storage.dtype)
+      values[page, :, p % ctx.page_size, :] = v.to(storage.dtype)
+    return q
+
+  def pool_blocks(self, storage, block_table, pool_storage, pool_table, ctx, num_kv_heads, head_dim, value_dim, pool):
+    ps = ctx.page_size
+    keys, values = self._kv_views(storage, num_kv_heads, ps, head_dim, value_dim)
+    pk, pv = self._kv_views(pool_storage, num_kv_heads, -(-ps // pool), head_dim, value_dim)
+    for b in range(ctx.num_seqs):
+      start = int(ctx.host["q_start"][b])
+      end = start + int(ctx.host["cu_q"][b + 1] - ctx.host["cu_q"][b])
+      for c in range(start // pool, end // pool):
+        j = torch.arange(c * pool, (c + 1) * pool, device=storage.device)
+        page = block_table[b, j // ps].long()
+        assert (page >= 0).all(), "a block would be pooled from a page its request does not hold"
+        to = int(pool_table[b, (c * pool) // ps])
+        assert to >= 0
+        e = ((c * pool) % ps) // pool
+        pk[to, :, e, :] = keys[page, :, j % ps, :].float().sum(0) / pool
+        pv[to, :, e, :] = values[page, :, j % ps, :].float().sum(0) / pool
+
+  def rotate_heads(self, x, positions, freq, num_heads, dim, inverse=False):
+    t = x.shape[0]
+    angle = (positions.float()[:, None] * freq[None, :])[:, None, :]
+    y = self._turn(x.float().reshape(t, num_heads, dim), -angle if inverse else angle)
+    return y.reshape(t, num_heads * dim).to(self.dtype)
+
+  def _general_attention(self, q, storage, block_table, ctx, num_heads, num_kv_heads, head_dim, value_dim,
+                         window, pooled):
+    t = q.shape[0]
+    ps = ctx.page_size
+    keys, values = self._kv_views(storage, num_kv_heads, ps, head_dim, value_dim)
+    group = num_heads // num_kv_heads
+    out = torch.zeros(t, num_heads, value_dim, dtype=torch.float32, device=q.device)
+    q = q.reshape(t, num_heads, head_dim)
+    for b in range(ctx.num_seqs):
+      r0, r1 = int(ctx.host["cu_q"][b]), int(ctx.host["cu_q"][b + 1])
+      start = int(ctx.host["q_start"][b])
+      for r in range(r0, r1):
+        i = start + r - r0
+        lo = 0 if window is None else max(i - window + 1, 0)
+        j = torch.arange(lo, i + 1, device=q.device)
+        page = block_table[b, j // ps].long()
+        assert (page >= 0).all(), "attention would read a page the request does not hold"
+        k = keys[page, :, j % ps, :].float()
+        v = values[page, :, j % ps, :].float()
+        if pooled is not None:
+          pool_storage, pool_table, pool = pooled
+          pk, pv = self._kv_views(pool_storage, num_kv_heads, -(-ps // pool), head_dim, value_dim)
+          nb = max((i - window + 1) // pool, 0)
+          if nb:
+            c = torch.arange(nb, device=q.device)
+            pg = pool_table[b, (c * pool) // ps].long()
+            assert (pg >= 0).all()
+            e = ((c * pool) % ps) // pool
+            k = torch.cat([pk[pg, :, e, :].float(), k], dim=0)
+            v = torch.cat([pv[pg, :, e, :].float(), v], dim=0)
+        for n in range(num_heads):
+          m = n // group
+          p = torch.softmax(k[:, m] @ q[r, n].float(), dim=0)
+          out[r, n] = p @ v[:, m]
+    return out.reshape(t, num_heads * value_dim).to(self.dtype)
+
+  # ---- gated delta rule -------------------------------------------------------
+  def delta_rule_inputs(self, pre, low, conv_weight, conv_state, decay_bias, neg_rate, ctx, *, conv_taps,
+                        num_heads, num_kv_heads, head_dim, value_dim):
+    t = pre.shape[0]
+    qk, vv = num_kv_heads * head_dim, num_heads * value_dim
+    c = 2 * qk + vv
+    x = pre[:, :c].float()
+    y = torch.empty_like(x)
+    for b in range(ctx.num_seqs):
+      r0, r1 = int(ctx.host["cu_q"][b]), int(ctx.host["cu_q"][b + 1])
+      slot = int(ctx.host["slots"][b])
+      seen = torch.cat([conv_state[slot].float(), x[r0:r1]], dim=0)  # [taps - 1 + n, C]
+      n = r1 - r0
+      y[r0:r1] = sum(seen[j:j + n] * conv_weight[:, j][None, :] for j in range(conv_taps))
+      if conv_taps > 1:
+        conv_state[slot] = seen[-(conv_taps - 1):]
+    y = y * torch.sigmoid(y)
+
+    def unit(z):
+      return z / torch.sqrt(z.pow(2).sum(-1, keepdim=True) + 1e-6)
+
+    q = unit(y[:, :qk].reshape(t, num_kv_heads, head_dim)) * head_dim ** -0.5
+    k = unit(y[:, qk:2 * qk].reshape(t, num_kv_heads, head_dim))
+    v = y[:, 2 * qk:c].reshape(t, num_heads, value_dim)
+    beta = torch.sigmoid(pre[:, c:c + num_heads].float())
+    a = low[:, :num_heads * head_dim].float() + decay_bias[None, :]
+    decay = torch.exp(neg_rate[None, :, None] * torch.nn.functional.softplus(a).reshape(t, num_heads, head_dim))
+    return q.contiguous(), k.contiguous(), v.contiguous(), decay.contiguous(), beta.contiguous()
+
+  def gated_delta_scan(self, q, k, v, decay, beta, state, ctx, *, num_heads, num_kv_heads, head_dim, value_dim):
+    out = torch.empty(q.shape[0], num_heads, value_dim, dtype=torch.float32, device=q.device)
+    rep = num_heads // num_kv_heads
+    for b in range(ctx.num_seqs):
+      r0, r1 = int(ctx.host["cu_q"][b]), int(ctx.host["cu_q"][b + 1])
+      slot = int(ctx.host["slots"][b])
+      for n in range(num_heads):
+        s = state[slot, n].clone()
+        for r in range(r0, r1):
+          s = decay[r, n][:, None] * s
+          u = beta[r, n] * (v[r, n] - s.t() @ k[r, n // rep])
+          s = s + torch.outer(k[r, n // rep], u)
+          out[r, n] = s.t() @ q[r, n // rep]
+        state[slot, n] = s
+    return out
+
+  def gated_head_norm(self, o, low, gate_offset, weight, eps, num_heads, value_dim):
+    t = o.shape[0]
+    y = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight.float()[None, None, :]
+    gate = torch.sigmoid(low[:, gate_offset:gate_offset + num_heads * value_dim].float())
+    return (y.reshape(t, num_heads * value_dim) * gate).to(self.dtype)
+
+  def normed_mean(self, branches, scales, eps):
+    total = 0
+    for x, w in zip(branches, scales):
+      total = total + self._rms(x, w, eps, False)
+    return (total / len(branches)).to(self.dtype)
 
   # ---- sampling -------------------------------------------------------------
   def token_logprobs(self, logits, tokens, temperature, top_k, top_p):
