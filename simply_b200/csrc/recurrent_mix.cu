@@ -14,6 +14,15 @@
 
 #define SB_ERR_BAD_SLOT 16  // a state slot outside the state tensor
 
+// A decode graph pads its batch by repeating the last request: only the first row of a slot
+// may write the slot's state (the others compute results that are dropped).
+__device__ __forceinline__ bool first_row_of_slot(const int* slots, int b) {
+  const int slot = slots[b];
+  for (int i = 0; i < b; ++i)
+    if (slots[i] == slot) return false;
+  return true;
+}
+
 __device__ __forceinline__ float sigmoid_f32(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
@@ -94,7 +103,7 @@ __global__ void conv_state_kernel(const T* __restrict__ pre, int pre_width, floa
   const int b = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int slot = slots[b];
-  if (c >= C || slot < 0 || slot >= num_slots) return;
+  if (c >= C || slot < 0 || slot >= num_slots || !first_row_of_slot(slots, b)) return;
   const int first = cu_q[b], n = cu_q[b + 1] - first;
   float* state = conv_state + (size_t)slot * (taps - 1) * C;
   for (int r = 0; r < taps - 1; ++r) {
@@ -224,7 +233,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
       if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = od;
     }
   }
-  if (on) {
+  if (on && first_row_of_slot(slots, b)) {
 #pragma unroll
     for (int r = 0; r < SCAN_ROWS; ++r) {
       const int row = rs + RS * r;

@@ -48,6 +48,8 @@ def _pad_rows(w: torch.Tensor, multiple: int = 8) -> torch.Tensor:
 @MIXERS.register("gated_delta_rule")
 class GatedDeltaRule(Mixer):
 
+  graph_safe = True  # reads the step's device tensors only; rows that repeat a slot do not write its state
+
   def __init__(self, prefix: str, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                value_dim: int, conv_taps: int, eps: float, decay_rank: int = -1, gate_rank: int = -1,
                names: dict[str, str] | None = None):

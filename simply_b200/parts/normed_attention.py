@@ -49,6 +49,8 @@ def rotation_frequencies(dims: int, base: float, factor: float = 1.0) -> np.ndar
 @MIXERS.register("qk_norm_attention")
 class QKNormAttention(Mixer):
 
+  graph_safe = True
+
   def __init__(self, prefix: str, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                score_scale: float, eps: float, value_dim: int | None = None, window: int | None = None,
                pool: int | None = None, rotary: dict | None = None, rotate_values: bool = False,

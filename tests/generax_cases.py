@@ -119,12 +119,12 @@ def as_numpy(t):
 
 
 def build_engine(cfg, tensors, dtype, device, ops, *, page_size=8, slots=4, max_cache_tokens=0, max_seq_len=256,
-                 poison=False, graphs=False):
+                 poison=False, graphs=False, burst=1):
   on_device = {k: v.to(device=device, dtype=getattr(torch, dtype) if v.is_floating_point() else v.dtype)
                for k, v in tensors.items()}
   ec = EngineConfig(activation_dtype=dtype, page_size=page_size, batch_size=slots, max_seq_len=max_seq_len,
                     max_cache_tokens=max_cache_tokens or slots * max_seq_len, max_window_cache_tokens=-1,
-                    poison_freed_pages=poison, use_cuda_graphs=graphs)
+                    poison_freed_pages=poison, use_cuda_graphs=graphs, intermediate_steps=burst)
   return Engine(cfg, on_device, ec, ops=ops, device=device)
 
 

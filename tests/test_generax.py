@@ -182,6 +182,26 @@ def test_greedy_generation_through_the_scheduler(where):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("which,burst", [("a", 1), ("b", 5)])
+def test_decoding_from_cuda_graphs(which, burst):
+  """Three live requests decode from the graph of four rows (the fourth repeats the third and
+  must not touch its state a second time), several steps per replay burst."""
+  cfg_dict = gx.CONFIG_A if which == "a" else gx.CONFIG_B
+  engine, t = engine_for(cfg_dict, ("float32", "cuda"), seed=13, slots=4, graphs=True, burst=burst)
+  assert engine._decode_runner is not None, "the model's parts must all allow graph capture"
+  w = gx.as_numpy(t)
+  prompts = [tokens_for(cfg_dict, n, 40 + i) for i, n in enumerate((9, 3, 14))]
+  results = engine.generate(prompts, SamplingParams(temperature=0.0, max_decode_steps=17))
+  assert engine._decode_runner.bursts > 0
+  for prompt, r in zip(prompts, results):
+    toks = list(prompt)
+    for _ in range(17):
+      toks.append(int(np.argmax(plain.forward(cfg_dict, w, toks)[-1])))
+    assert r.output_token_ids == toks[len(prompt):], (r.output_token_ids, toks[len(prompt):])
+  engine.ops.check_errors()
+
+
+@pytest.mark.gpu
 def test_bfloat16_generation_runs_and_samples():
   engine, _ = engine_for(gx.CONFIG_A, ("bfloat16", "cuda"), seed=2, slots=3)
   prompts = [tokens_for(gx.CONFIG_A, n, i) for i, n in enumerate((4, 30, 11, 2, 19))]
