@@ -59,6 +59,11 @@ struct AttnParams {
   int rows_max;
   int older_keys_settled;  // decode: keys below q_start were written before the kernel just before this one
   int* err;
+  // prefill, optional: one key and value per whole block of `pool_len` tokens that has left the
+  // window, [P', 2, Hkv, pool_entries, DH], entry of block c in the page of token c * pool_len
+  const bf16* pool;
+  const int* pool_table;
+  int pool_max_pages, pool_len, pool_entries, pool_pages;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -140,6 +145,38 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, bf16* sk, bf16
   }
 }
 
+// The same for block entries [tile, tile + TILE) of the pooled storage (entries from `num_blocks`
+// on are zero-filled).  Contains one __syncthreads.
+template <int TILE, int THREADS>
+__device__ __forceinline__ void load_pool_tile(const AttnParams& p, bf16* sk, bf16* sv, long long* row_src,
+                                               int tile, int num_blocks, int b, int m) {
+  const size_t head_stride = (size_t)p.pool_entries * DH;
+  const size_t v_offset = (size_t)p.num_kv_heads * head_stride;
+  for (int row = threadIdx.x; row < TILE; row += THREADS) {
+    const int c = tile + row;
+    long long src = -1;
+    if (c < num_blocks) {
+      const long long start = (long long)c * p.pool_len;
+      const long long page = p.pool_table[(size_t)b * p.pool_max_pages + start / p.page_size];
+      if (page < 0 || page >= p.pool_pages)
+        atomicOr(p.err, SB_ERR_BAD_PAGE);
+      else
+        src = (long long)(((size_t)page * 2 * p.num_kv_heads + m) * head_stride +
+                          (size_t)((start % p.page_size) / p.pool_len) * DH);
+    }
+    row_src[row] = src;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < TILE * CPR; i += THREADS) {
+    const int row = i / CPR, c = i - row * CPR;
+    const long long src = row_src[row];
+    const bool valid = src >= 0;
+    const bf16* g = p.pool + (valid ? src : 0) + c * 8;
+    cp_async16(sk + row * PITCH + c * 8, g, valid);
+    cp_async16(sv + row * PITCH + c * 8, g + v_offset, valid);
+  }
+}
+
 // Scores of one warp's 16 query rows against NKT * 8 keys that start at row `key0` of the tile.
 template <int NKT>
 __device__ __forceinline__ void scores(float (&s)[NKT][4], const bf16* sq_rows, const bf16* sk, int key0) {
@@ -168,7 +205,10 @@ __device__ __forceinline__ void scores(float (&s)[NKT][4], const bf16* sq_rows, 
 template <int NKT>
 __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8][4], float& m_a, float& m_b,
                                            float& l_a, float& l_b, int pos_a, int pos_b, int j0, float cap,
-                                           int window, const bf16* sv, int key0, bool need_mask = true) {
+                                           int window, const bf16* sv, int key0, bool need_mask = true,
+                                           int pool_len = 0) {
+  // pool_len > 0: the keys are block entries j0, j0 + 1, ...; a row at `pos` sees the blocks that
+  // lie wholly before its window, j < (pos - window + 1) / pool_len.
   const int lane = threadIdx.x & 31, t = lane & 3;
   const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
   float mx_a = -INFINITY, mx_b = -INFINITY;
@@ -181,7 +221,8 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NKT][4], float (&o)[DH / 8
       float v = s[i][e];
       if (cap > 0.f) v = cap * fast_tanh(v * inv_cap);
       // need_mask is false (for the whole warp) when every key of the tile is visible to every row.
-      const bool keep = !need_mask || (j <= pos && (window <= 0 || pos - j < window));
+      const bool keep = pool_len > 0 ? (pos - window + 1 > 0 && j < (pos - window + 1) / pool_len)
+                                     : (!need_mask || (j <= pos && (window <= 0 || pos - j < window)));
       v = keep ? v * LOG2E : -INFINITY;
       s[i][e] = v;
       if (e < 2) mx_a = fmaxf(mx_a, v); else mx_b = fmaxf(mx_b, v);
@@ -270,7 +311,17 @@ __global__ void __launch_bounds__(WM * WN * 32) attn_prefill_kernel(const AttnPa
   const int kv_hi = p1 + 1;
   const int tile0 = (lo / BN) * BN;
   const int n_tiles = (kv_hi - tile0 + BN - 1) / BN;
-  load_kv_tile<BN, THREADS>(p, sk, sv, row_src[0], tile0, kv_lo, kv_hi, b, m);
+  // Block entries that the tile's last row sees come first, in tiles of their own.
+  const int n_blocks = (p.pool != nullptr && p.window > 0 && p1 - p.window + 1 > 0) ? (p1 - p.window + 1) / p.pool_len : 0;
+  const int n_pool_tiles = (n_blocks + BN - 1) / BN;
+  auto load_tile = [&](int it, int stage) {
+    if (it < n_pool_tiles)
+      load_pool_tile<BN, THREADS>(p, sk + stage * BN * PITCH, sv + stage * BN * PITCH, row_src[stage], it * BN, n_blocks, b, m);
+    else
+      load_kv_tile<BN, THREADS>(p, sk + stage * BN * PITCH, sv + stage * BN * PITCH, row_src[stage],
+                                tile0 + (it - n_pool_tiles) * BN, kv_lo, kv_hi, b, m);
+  };
+  load_tile(0, 0);
   cp_async_commit();
 
   const int ra = wm * 16 + g, rb = ra + 8;
@@ -284,25 +335,26 @@ __global__ void __launch_bounds__(WM * WN * 32) attn_prefill_kernel(const AttnPa
 #pragma unroll
   for (int d = 0; d < DH / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
-  for (int it = 0; it < n_tiles; ++it) {
+  for (int it = 0; it < n_pool_tiles + n_tiles; ++it) {
     const int stage = it & 1;
-    if (it + 1 < n_tiles) {
-      load_kv_tile<BN, THREADS>(p, sk + (stage ^ 1) * BN * PITCH, sv + (stage ^ 1) * BN * PITCH, row_src[stage ^ 1],
-                                tile0 + (it + 1) * BN, kv_lo, kv_hi, b, m);
+    if (it + 1 < n_pool_tiles + n_tiles) {
+      load_tile(it + 1, stage ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    const int j0 = tile0 + it * BN + wn * KEYS;  // this warp's first key of the tile
+    const bool pooled = it < n_pool_tiles;
+    // this warp's first key of the tile (its first block entry, in a tile of those)
+    const int j0 = (pooled ? it * BN : tile0 + (it - n_pool_tiles) * BN) + wn * KEYS;
     // Every key visible to every row of the warp: below the lowest row's position, inside the
     // highest row's window.
     const bool need_mask = !rows_full || j0 + KEYS - 1 > warp_pos_lo || (p.window > 0 && warp_pos_hi - j0 >= p.window);
     float s[KEYS / 8][4];
     scores<KEYS / 8>(s, sq + wm * 16 * PITCH, sk + stage * BN * PITCH, wn * KEYS);
     softmax_pv<KEYS / 8>(s, o, m_a, m_b, l_a, l_b, pos_a, pos_b, j0, p.cap, p.window, sv + stage * BN * PITCH,
-                         wn * KEYS, need_mask);
+                         wn * KEYS, need_mask, pooled ? p.pool_len : 0);
     __syncthreads();
   }
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -1278,18 +1330,23 @@ static int blocks_resident(Kernel kernel, int threads, size_t smem, int* out) {
 // Ragged prefill attention.  items: [num_items, 2] (sequence, first token of a tile of
 // rows_per_tile / G tokens); rows_per_tile is 64 or 128.  Tiles of 64 rows run with two key
 // groups (8 warps) unless single_key_group is set.
-extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const int* block_table, int max_pages,
-                                      const int* cu_q, const int* q_start, void* out, int num_q_heads,
-                                      int num_kv_heads, int page_size, int num_pages, float cap, int window,
-                                      const int* items, int num_items, int rows_per_tile, int single_key_group,
-                                      int* err, cudaStream_t stream) {
+// With `pool`: block entries of `pool_len` tokens ahead of the window (see AttnParams).
+extern "C" int SB_FN(sb_attn_prefill_pooled)(const void* q, const void* cache, const int* block_table, int max_pages,
+                                             const int* cu_q, const int* q_start, void* out, int num_q_heads,
+                                             int num_kv_heads, int page_size, int num_pages, float cap, int window,
+                                             const int* items, int num_items, int rows_per_tile, int single_key_group,
+                                             const void* pool, const int* pool_table, int pool_max_pages, int pool_len,
+                                             int pool_pages, int* err, cudaStream_t stream) {
   if (num_items == 0) return 0;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_q_heads / num_kv_heads > rows_per_tile) return -8;
+  if (pool != nullptr && (pool_len <= 0 || window <= 0)) return -8;
   AttnParams p{};
   p.q = (const bf16*)q; p.cache = (const bf16*)cache; p.block_table = block_table; p.max_pages = max_pages;
   p.cu_q = cu_q; p.q_start = q_start; p.out = (bf16*)out; p.num_q_heads = num_q_heads;
   p.num_kv_heads = num_kv_heads; p.page_size = page_size; p.num_pages = num_pages; p.cap = cap;
   p.window = window; p.items = items; p.err = err;
+  p.pool = (const bf16*)pool; p.pool_table = pool_table; p.pool_max_pages = pool_max_pages; p.pool_len = pool_len;
+  p.pool_entries = pool_len > 0 ? (page_size + pool_len - 1) / pool_len : 0; p.pool_pages = pool_pages;
   // The merge of two key groups needs [BM][DH] floats where the tiles were.
   constexpr bool split_fits = (size_t)(2 * 64 + 64 * DH) * sizeof(float) <= (size_t)4 * BN * PITCH * sizeof(bf16);
   if (rows_per_tile == 128) {
@@ -1324,6 +1381,16 @@ extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const in
   }
   SB_LAUNCH_CHECK();
   return 0;
+}
+
+extern "C" int SB_FN(sb_attn_prefill)(const void* q, const void* cache, const int* block_table, int max_pages,
+                                      const int* cu_q, const int* q_start, void* out, int num_q_heads,
+                                      int num_kv_heads, int page_size, int num_pages, float cap, int window,
+                                      const int* items, int num_items, int rows_per_tile, int single_key_group,
+                                      int* err, cudaStream_t stream) {
+  return SB_FN(sb_attn_prefill_pooled)(q, cache, block_table, max_pages, cu_q, q_start, out, num_q_heads, num_kv_heads,
+                                       page_size, num_pages, cap, window, items, num_items, rows_per_tile,
+                                       single_key_group, nullptr, nullptr, 0, 0, 0, err, stream);
 }
 
 // Split-key attention for sequences with at most 16 query rows per kv head, and the merge.

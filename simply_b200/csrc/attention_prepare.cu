@@ -125,13 +125,13 @@ extern "C" int sb_qk_norm_rotate_store(const void* qkv, int row_width, int dtype
 
 // ---------------------------------------------------------------------------
 // Pooled blocks: for every block of P tokens whose last token arrived in this step, the mean of
-// its keys and of its values as the cache holds them, summed in the tokens' order, into the
-// float32 storage of block entries.  Grid (block within the step, sequence, kv head).
+// its keys and of its values as the cache holds them, summed in float32 in the tokens' order,
+// into the storage of block entries.  Grid (block within the step, sequence, kv head).
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
 pool_blocks_kernel(const T* __restrict__ cache, const int* __restrict__ block_table, int max_pages, int num_pages,
-                   float* __restrict__ pool, const int* __restrict__ pool_table, int pool_max_pages,
+                   T* __restrict__ pool, const int* __restrict__ pool_table, int pool_max_pages,
                    int pool_pages, const int* __restrict__ cu_q, const int* __restrict__ q_start, int G, int d,
                    int dv, int page_size, int P, int* err) {
   pdl_wait_block();
@@ -167,13 +167,13 @@ pool_blocks_kernel(const T* __restrict__ cache, const int* __restrict__ block_ta
       atomicOr(err, SB_ERR_BAD_PAGE);
       continue;
     }
-    float* dst = pool + to * pool_stride + (is_key ? 0 : (size_t)G * entries * d) + entry * width + cc;
-    *dst = sum / (float)P;
+    T* dst = pool + to * pool_stride + (is_key ? 0 : (size_t)G * entries * d) + entry * width + cc;
+    *dst = from_f32<T>(sum / (float)P);
   }
 }
 
 extern "C" int sb_pool_blocks(const void* cache, int dtype, const int* block_table, int max_pages, int num_pages,
-                              float* pool, const int* pool_table, int pool_max_pages, int pool_pages,
+                              void* pool, const int* pool_table, int pool_max_pages, int pool_pages,
                               const int* cu_q, const int* q_start, int num_seqs, int max_blocks, int G, int d,
                               int dv, int page_size, int P, int* err, cudaStream_t stream) {
   if (num_seqs == 0 || max_blocks <= 0) return 0;
@@ -181,10 +181,10 @@ extern "C" int sb_pool_blocks(const void* cache, int dtype, const int* block_tab
   const dim3 grid(max_blocks, num_seqs, G);
   if (dtype == SB_DTYPE_F32)
     sb_launch(pool_blocks_kernel<float>, grid, 128, 0, stream, (const float*)cache, block_table, max_pages,
-              num_pages, pool, pool_table, pool_max_pages, pool_pages, cu_q, q_start, G, d, dv, page_size, P, err);
+              num_pages, (float*)pool, pool_table, pool_max_pages, pool_pages, cu_q, q_start, G, d, dv, page_size, P, err);
   else
     sb_launch(pool_blocks_kernel<bf16>, grid, 128, 0, stream, (const bf16*)cache, block_table, max_pages,
-              num_pages, pool, pool_table, pool_max_pages, pool_pages, cu_q, q_start, G, d, dv, page_size, P, err);
+              num_pages, (bf16*)pool, pool_table, pool_max_pages, pool_pages, cu_q, q_start, G, d, dv, page_size, P, err);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -153,10 +153,18 @@ extern "C" int sb_delta_inputs(const void* pre, int pre_width, const void* low, 
 // tokens of this step in order.  A column of S is held by RS neighbouring lanes, each with the
 // rows rs, rs + RS, ... (at most 32) in registers; the two sums over rows per token are
 // butterfly sums over those lanes, in an order that does not depend on the step's shape.  k, q,
-// g, v and beta of SCAN_CHUNK tokens at a time are staged in shared memory.
+// g, v and beta of SCAN_CHUNK tokens at a time come to shared memory by cp.async, the next
+// chunk while the block works on this one.
 // ---------------------------------------------------------------------------
 #define SCAN_CHUNK 8
 #define SCAN_ROWS 32
+
+__device__ __forceinline__ void scan_copy4(float* smem, const float* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void scan_copy16(float* smem, const float* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
 
 template <int RS>
 __global__ void __launch_bounds__(128)
@@ -166,7 +174,8 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
                   int dv, int cols, float* __restrict__ out, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
-  extern __shared__ float stage[];  // SCAN_CHUNK * (3 d + cols + 1)
+  // Two buffers of: k [CHUNK][d], q [CHUNK][d], g [CHUNK][d], v [CHUNK][cols], beta [CHUNK].
+  extern __shared__ __align__(16) float stage[];
   const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
   const int rs = threadIdx.x % RS, col_local = threadIdx.x / RS;
   const int col = col0 + col_local;
@@ -178,6 +187,42 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     return;
   }
   const int g_head = h / (H / G);
+  const int cols_pad = (cols + 3) & ~3;
+  const int buffer = SCAN_CHUNK * (3 * d + cols_pad + 4);
+  const bool vec = (d & 3) == 0;
+
+  auto issue = [&](int which, int base) {
+    float* buf = stage + which * buffer;
+    const int count = min(SCAN_CHUNK, n - base);
+    if (vec) {
+      const int d4 = d >> 2;
+      for (int idx = threadIdx.x; idx < count * 3 * d4; idx += blockDim.x) {
+        const int i = idx / (3 * d4), rem = idx - i * 3 * d4, kind = rem / d4, c = (rem - kind * d4) * 4;
+        const size_t t = (size_t)(first + base + i);
+        const float* src = kind == 0 ? k + (t * G + g_head) * d : kind == 1 ? q + (t * G + g_head) * d
+                                                                             : decay + (t * H + h) * d;
+        scan_copy16(buf + (kind * SCAN_CHUNK + i) * d + c, src + c);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < count * 3 * d; idx += blockDim.x) {
+        const int i = idx / (3 * d), rem = idx - i * 3 * d, kind = rem / d, c = rem - kind * d;
+        const size_t t = (size_t)(first + base + i);
+        const float* src = kind == 0 ? k + (t * G + g_head) * d : kind == 1 ? q + (t * G + g_head) * d
+                                                                             : decay + (t * H + h) * d;
+        scan_copy4(buf + (kind * SCAN_CHUNK + i) * d + c, src + c);
+      }
+    }
+    float* bv = buf + 3 * SCAN_CHUNK * d;
+    for (int idx = threadIdx.x; idx < count * cols; idx += blockDim.x) {
+      const int i = idx / cols, c = idx - i * cols;
+      scan_copy4(bv + i * cols_pad + c, v + ((size_t)(first + base + i) * H + h) * dv + min(col0 + c, dv - 1));
+    }
+    float* bb = bv + SCAN_CHUNK * cols_pad;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) scan_copy4(bb + i, beta + (size_t)(first + base + i) * H + h);
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+
+  if (n > 0) issue(0, 0);
   float* S = state + ((size_t)slot * H + h) * d * dv;
   float s[SCAN_ROWS];
 #pragma unroll
@@ -185,28 +230,23 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
     const int row = rs + RS * r;
     s[r] = (on && row < d) ? S[(size_t)row * dv + col] : 0.f;
   }
-  const int per_token = 3 * d + cols + 1;
-  for (int base = 0; base < n; base += SCAN_CHUNK) {
+  int which = 0;
+  for (int base = 0; base < n; base += SCAN_CHUNK, which ^= 1) {
     const int count = min(SCAN_CHUNK, n - base);
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < count * per_token; idx += blockDim.x) {
-      const int i = idx / per_token, e = idx % per_token;
-      const size_t t = (size_t)(first + base + i);
-      float x;
-      if (e < d) x = k[(t * G + g_head) * d + e];
-      else if (e < 2 * d) x = q[(t * G + g_head) * d + (e - d)];
-      else if (e < 3 * d) x = decay[(t * H + h) * d + (e - 2 * d)];
-      else if (e < 3 * d + cols) x = (col0 + e - 3 * d) < dv ? v[(t * H + h) * dv + col0 + (e - 3 * d)] : 0.f;
-      else x = beta[t * H + h];
-      stage[idx] = x;
+    if (base + SCAN_CHUNK < n) {
+      issue(which ^ 1, base + SCAN_CHUNK);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
     }
     __syncthreads();
+    const float* buf = stage + which * buffer;
     for (int i = 0; i < count; ++i) {
-      const float* kk = stage + i * per_token;
-      const float* qq = kk + d;
-      const float* gg = kk + 2 * d;
-      const float vv = kk[3 * d + min(col_local, cols - 1)];
-      const float bb = kk[3 * d + cols];
+      const float* kk = buf + i * d;
+      const float* qq = buf + (SCAN_CHUNK + i) * d;
+      const float* gg = buf + (2 * SCAN_CHUNK + i) * d;
+      const float vv = buf[3 * SCAN_CHUNK * d + i * cols_pad + min(col_local, cols - 1)];
+      const float bb = buf[3 * SCAN_CHUNK * d + SCAN_CHUNK * cols_pad + i];
       float dot = 0.f;
 #pragma unroll
       for (int r = 0; r < SCAN_ROWS; ++r) {
@@ -232,6 +272,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
       for (int o = 1; o < RS; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
       if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = od;
     }
+    __syncthreads();  // the buffer is filled again two chunks on
   }
   if (on && first_row_of_slot(slots, b)) {
 #pragma unroll
@@ -252,14 +293,20 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
   const int threads = 128;
   int cols = threads / rs;
   if (cols > dv) cols = dv;
-  // Few (sequence, head) pairs: narrower blocks, so that more SMs share the columns.
-  while (cols > 8 && (long long)num_seqs * H * ((dv + cols - 1) / cols) < 296) cols = (cols + 1) / 2;
+  // Few (sequence, head) pairs: narrower blocks, so that more SMs share the columns (not below
+  // 64 threads: a block's threads also fetch its chunks).
+  while (cols * rs > 64 && (long long)num_seqs * H * ((dv + cols - 1) / cols) < 148) cols = (cols + 1) / 2;
   const int block = ((cols * rs + 31) / 32) * 32;
   const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
-  const size_t smem = (size_t)SCAN_CHUNK * (3 * d + cols + 1) * sizeof(float);
+  const size_t smem = (size_t)2 * SCAN_CHUNK * (3 * d + ((cols + 3) & ~3) + 4) * sizeof(float);
+  if (smem > 200 * 1024) return -13;
 #define SB_SCAN(RS_)                                                                                          \
-  sb_launch(delta_scan_kernel<RS_>, grid, block, smem, stream, q, k, v, decay, beta, state, cu_q, slots,     \
-            num_slots, G, H, d, dv, cols, out, err)
+  do {                                                                                                        \
+    if (smem > 48 * 1024)                                                                                     \
+      cudaFuncSetAttribute(delta_scan_kernel<RS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+    sb_launch(delta_scan_kernel<RS_>, grid, block, smem, stream, q, k, v, decay, beta, state, cu_q, slots,   \
+              num_slots, G, H, d, dv, cols, out, err);                                                        \
+  } while (0)
   switch (rs) {
     case 1: SB_SCAN(1); break;
     case 2: SB_SCAN(2); break;

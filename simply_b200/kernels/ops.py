@@ -225,7 +225,7 @@ class CudaOps:
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_paged_attention_general": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void,
-                                       c_int, c_int, c_int, c_void, c_void],
+                                       c_int, c_int, c_int, c_void, c_void, c_void],
         "sb_qk_norm_rotate_store": [c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_int, c_void,
                                     c_void, c_void, c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_void, c_void],
@@ -326,6 +326,9 @@ class CudaOps:
       prefill.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
                           c_float, c_int, c_void, c_int, c_int, c_int, c_void, c_void]
       prefill.restype = c_int
+      prefill_pooled = getattr(lib, f"sb_attn_prefill_pooled_hd{head_dim}")
+      prefill_pooled.argtypes = prefill.argtypes[:-2] + [c_void, c_void, c_int, c_int, c_int, c_void, c_void]
+      prefill_pooled.restype = c_int
       decode = getattr(lib, f"sb_attn_decode_hd{head_dim}")
       decode.argtypes = [c_void, c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
                          c_int, c_int, c_float, c_int, c_void, c_int, c_int, c_void, c_void, c_void, c_int,
@@ -352,7 +355,7 @@ class CudaOps:
       if slots <= 0:
         raise KernelError(f"sb_attn_decode_resident: {_STATUS.get(slots, slots)}")
       self._decode_slots[head_dim] = slots
-      fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc, prefill_pair)
+      fns = self._attn_fns[head_dim] = (prefill, decode, make_map, prefill_tc, prefill_pair, prefill_pooled)
     return fns
 
   def decode_chunk_for(self, kv_lo: Sequence[int], kv_hi: Sequence[int], num_kv_heads: int, head_dim: int) -> int:
@@ -467,7 +470,7 @@ class CudaOps:
     return AttentionGraphPlan(self, window, group, num_kv_heads, head_dim, batch, bucket, max_burst, page_size)
 
   def _attention_plan(self, ctx: Any, window: int | None, group: int, force_rows: int = 0,
-                      num_kv_heads: int = 1, head_dim: int = 0) -> dict:
+                      num_kv_heads: int = 1, head_dim: int = 0, tag: tuple = ()) -> dict:
     """Work lists of the two tensor-core kernels for this step, per kind of layer (`_plan_key`).
 
     Sequences with at most 16 query rows per kv head (one or a few new tokens) go to the
@@ -475,7 +478,7 @@ class CudaOps:
     absolute position, one work item per chunk.  The others are cut into tiles of
     64 // group or 128 // group tokens for the prefill kernel, heaviest tile first.
     """
-    key = self._plan_key(window, group, num_kv_heads, head_dim, ctx.page_size)
+    key = self._plan_key(window, group, num_kv_heads, head_dim, ctx.page_size) + tag
     plan = ctx.memo.get(key)
     if plan is not None:
       return plan
@@ -758,16 +761,47 @@ class CudaOps:
     group = num_heads // num_kv_heads
     if pooled is not None or value_dim != head_dim:
       pool, pool_table, pool_len = pooled if pooled is not None else (None, None, 0)
-      if pool is not None and pool.dtype != torch.float32:
-        raise KernelError("block entries are kept in float32")
-      self._call("sb_paged_attention_general", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
-                 block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
-                 num_kv_heads, head_dim, value_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
-                 int(window or 0), _ptr(pool), _ptr(pool_table), pool_table.shape[1] if pool is not None else 0,
-                 int(pool_len), pool.shape[0] if pool is not None else 0, _ptr(self.err))
+      if pool is not None and pool.dtype != storage.dtype:
+        raise KernelError("block entries and the cache must share one dtype")
+      pool_args = (_ptr(pool), _ptr(pool_table), pool_table.shape[1] if pool is not None else 0, int(pool_len),
+                   pool.shape[0] if pool is not None else 0)
+
+      def general(token_list, count):
+        self._call("sb_paged_attention_general", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
+                   block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), count, num_heads,
+                   num_kv_heads, head_dim, value_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
+                   int(window or 0), *pool_args, _ptr(token_list), _ptr(self.err))
+
+      # Portions of prompts go to the tensor-core kernel (mma.sync tiles of 64 rows, the block
+      # entries in tiles of their own ahead of the tokens); sequences that bring a token or a few,
+      # and shapes that kernel does not take, to the general one.
+      tensor_cores = (value_dim == head_dim and q.dtype == torch.bfloat16 and window
+                      and self._uses_tensor_core_attention(head_dim, group) and ctx.max_q_len * group > 16
+                      and "cu_q" in ctx.host)
+      if not tensor_cores:
+        general(None, t)
+        return out
+      plan = self._attention_plan(ctx, window, group, 0, num_kv_heads, head_dim, tag=("pooled", pool_len))
+      if plan["num_prefill"]:
+        rc = self._attention_lib(head_dim)[5](
+            _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q), _ptr(ctx.q_start),
+            _ptr(out), num_heads, num_kv_heads, ctx.page_size, storage.shape[0], float(logit_softcap), int(window),
+            _ptr(plan["prefill_items"]), plan["num_prefill"], plan["rows_per_tile"], int(self.prefill_single_key_group),
+            *pool_args, _ptr(self.err), self._stream())
+        self.launches += 1
+        if rc:
+          raise KernelError(f"sb_attn_prefill_pooled: {_STATUS.get(rc, rc)}")
+      if plan["num_decode"]:
+        rows = ctx.memo.get(("few_token_rows", group))
+        if rows is None:
+          cu_q = ctx.host["cu_q"]
+          few = [np.arange(cu_q[b], cu_q[b + 1]) for b in range(ctx.num_seqs) if (cu_q[b + 1] - cu_q[b]) * group <= 16]
+          rows = ctx.memo[("few_token_rows", group)] = torch.from_numpy(
+              np.concatenate(few).astype(np.int32)).to(self.device, non_blocking=True)
+        general(rows, rows.numel())
       return out
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
-      prefill, decode, _, prefill_tc, prefill_pair = self._attention_lib(head_dim)
+      prefill, decode, _, prefill_tc, prefill_pair = self._attention_lib(head_dim)[:5]
       use_tc = prefill_tc is not None and self._prefill_uses_tcgen05(head_dim, group, ctx.page_size)
       use_pair = prefill_pair is not None and self._prefill_uses_pairs(head_dim, group, ctx.page_size)
       plan = self._attention_plan(ctx, window, group, 256 if use_pair else (128 if use_tc else 0), num_kv_heads, head_dim)

@@ -16,7 +16,7 @@ any of these, each switched by a parameter:
   value per whole block of P tokens that has left the window: block b (tokens bP .. bP + P - 1) is
   seen from position i when bP + P - 1 <= i - window, as the mean of its keys and of its values
   as the cache holds them; tokens and blocks share one softmax.  The block means live in a
-  second paged cache with one entry per P tokens, which keeps every block (float32);
+  second paged cache with one entry per P tokens, which keeps every block;
 * `project_kv=False`: the layer has no k/v tensors and reads the cache another layer writes.
 
 The cache of a layer with a window keeps `cache_window` tokens (at least the window and a
@@ -96,7 +96,7 @@ class QKNormAttention(Mixer):
     if self.pool is None:
       return kv
     return {"kv": kv, "pool": PagedKVNeed(self.num_kv_heads, self.head_dim, None, value_dim=value_dim,
-                                          stride=self.pool, dtype="float32")}
+                                          stride=self.pool)}
 
   def graph_plans(self, ops, batch: int, bucket: int, max_burst: int, page_size: int) -> list:
     if self.pool is not None or self.value_dim != self.head_dim:
