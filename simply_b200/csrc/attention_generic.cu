@@ -1,7 +1,8 @@
 // Ragged paged attention, general form: any head size, page size, grouping and
-// storage type.  One warp per (token, query head); keys are visited in tiles of
-// 32 that start at a multiple of 32 of the absolute key position, so a token's
-// result is the same whatever else the step holds.
+// storage type.  One block of four warps per (token, query head); keys are visited in
+// tiles of 32 that start at a multiple of 32 of the absolute key position, tile number i
+// by warp i mod 4, and the warps' parts are merged in warp order, so a token's result is
+// the same whatever else the step holds.
 //
 //   s = q . k                 (q is already rotated and scaled)
 //   s = cap * tanh(s / cap)   if cap > 0          simply/model_lib.py:621-626
@@ -80,14 +81,28 @@ __device__ __forceinline__ void gen_tile(const KT* kr, const KT* vr, const float
 #pragma unroll
   for (int i = 0; i < GEN_MAX_DPL; ++i) acc[i] *= alpha;
   const unsigned valid_mask = __ballot_sync(0xffffffffu, valid);
-  for (int jj = 0; jj < 32; ++jj) {
-    if (!((valid_mask >> jj) & 1u)) continue;  // uniform over the warp
-    const float pj = __shfl_sync(0xffffffffu, p, jj);
-    const KT* vj = reinterpret_cast<const KT*>(__shfl_sync(0xffffffffu, (unsigned long long)vr, jj));
+  // Four keys at a time: their values are fetched together, then added in the keys' order.
+  for (int j0 = 0; j0 < 32; j0 += 4) {
+    const unsigned four = (valid_mask >> j0) & 0xfu;  // uniform over the warp
+    if (!four) continue;
+    float pj[4];
+    const KT* vj[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      pj[u] = __shfl_sync(0xffffffffu, p, j0 + u);
+      vj[u] = reinterpret_cast<const KT*>(__shfl_sync(0xffffffffu, (unsigned long long)vr, j0 + u));
+    }
 #pragma unroll
     for (int i = 0; i < GEN_MAX_DPL; ++i) {
       const int d = lane + 32 * i;
-      if (d < v_dim) acc[i] = fmaf(pj, to_f32<KT>(vj[d]), acc[i]);
+      if (d < v_dim) {
+        float x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) x[u] = ((four >> u) & 1u) ? to_f32<KT>(vj[u][d]) : 0.f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if ((four >> u) & 1u) acc[i] = fmaf(pj[u], x[u], acc[i]);
+      }
     }
   }
 }
@@ -104,18 +119,19 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
                                const int* __restrict__ token_list, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
-  extern __shared__ float smem[];  // per warp: head_dim floats of q
+  // head_dim floats of q, then per warp its running maximum, sum and v_dim partial results
+  extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long item = (long long)blockIdx.x * GEN_WARPS + warp;
-  if (item >= (long long)num_tokens * num_q_heads) return;
+  const long long item = blockIdx.x;
   const int listed = (int)(item / num_q_heads), n = (int)(item % num_q_heads);
   const int t = token_list != nullptr ? token_list[listed] : listed;
   const int m = n / (num_q_heads / num_kv_heads);
   const int b = token_seq[t], pos = positions[t];
-  float* qs = smem + warp * head_dim;
+  float* qs = smem;
+  float* part = smem + head_dim;
   const T* qp = q + ((size_t)t * num_q_heads + n) * head_dim;
-  for (int d = lane; d < head_dim; d += 32) qs[d] = to_f32<T>(qp[d]);
-  __syncwarp();
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) qs[d] = to_f32<T>(qp[d]);
+  __syncthreads();
 
   const int lo = window > 0 ? max(pos - window + 1, 0) : 0;
   float m_run = -0.5f * FLT_MAX, l_run = 0.f;
@@ -128,7 +144,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
     const int num_blocks = pos - window + 1 > 0 ? (pos - window + 1) / pool_len : 0;
     const int entries = (page_size + pool_len - 1) / pool_len;
     const size_t page_stride = (size_t)num_kv_heads * entries * (head_dim + v_dim);
-    for (int tile = 0; tile < num_blocks; tile += 32) {
+    for (int tile = 32 * warp; tile < num_blocks; tile += 32 * GEN_WARPS) {  // tile i belongs to warp i % 4
       const int c = tile + lane;
       const T* kr = nullptr;
       const T* vr = nullptr;
@@ -150,6 +166,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
   const size_t page_stride = (size_t)num_kv_heads * page_size * (head_dim + v_dim);
   const size_t value_base = (size_t)num_kv_heads * page_size * head_dim;
   for (int tile = (lo / 32) * 32; tile <= pos; tile += 32) {
+    if (((tile >> 5) & (GEN_WARPS - 1)) != warp) continue;  // by the tile's absolute number
     const int j = tile + lane;
     const T* kr = nullptr;
     const T* vr = nullptr;
@@ -165,12 +182,35 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
     }
     gen_tile<T>(kr, vr, qs, head_dim, v_dim, cap, lane, m_run, l_run, acc);
   }
-  T* op = out + ((size_t)t * num_q_heads + n) * v_dim;
-  const float inv = 1.0f / l_run;
+  // The warps' parts meet in warp order (the same order whatever the step holds).
+  float* mine = part + (size_t)warp * (v_dim + 2);
+  if (lane == 0) {
+    mine[0] = m_run;
+    mine[1] = l_run;
+  }
 #pragma unroll
   for (int i = 0; i < GEN_MAX_DPL; ++i) {
     const int d = lane + 32 * i;
-    if (d < v_dim) op[d] = from_f32<T>(acc[i] * inv);
+    if (d < v_dim) mine[2 + d] = acc[i];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float m_all = part[0];
+#pragma unroll
+  for (int w = 1; w < GEN_WARPS; ++w) m_all = fmaxf(m_all, part[(size_t)w * (v_dim + 2)]);
+  float scale[GEN_WARPS], l_all = 0.f;
+#pragma unroll
+  for (int w = 0; w < GEN_WARPS; ++w) {
+    scale[w] = expf(part[(size_t)w * (v_dim + 2)] - m_all);
+    l_all += part[(size_t)w * (v_dim + 2) + 1] * scale[w];
+  }
+  T* op = out + ((size_t)t * num_q_heads + n) * v_dim;
+  const float inv = 1.0f / l_all;
+  for (int d = lane; d < v_dim; d += 32) {
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < GEN_WARPS; ++w) sum += part[(size_t)w * (v_dim + 2) + 2 + d] * scale[w];
+    op[d] = from_f32<T>(sum * inv);
   }
 }
 
@@ -185,8 +225,9 @@ extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* 
   if (head_dim <= 0 || head_dim > 32 * GEN_MAX_DPL || v_dim <= 0 || v_dim > 32 * GEN_MAX_DPL) return -7;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return -8;
   const long long items = (long long)num_tokens * num_q_heads;
-  const unsigned blocks = (unsigned)((items + GEN_WARPS - 1) / GEN_WARPS);
-  const size_t smem = (size_t)GEN_WARPS * head_dim * sizeof(float);
+  if (items > 0x7fffffffLL) return -6;
+  const unsigned blocks = (unsigned)items;
+  const size_t smem = ((size_t)head_dim + (size_t)GEN_WARPS * (v_dim + 2)) * sizeof(float);
   if (dtype == SB_DTYPE_F32)
     sb_launch(paged_attention_generic_kernel<float>, blocks, GEN_WARPS * 32, smem, stream, (const float*)q,
         (const float*)cache, block_table, max_pages, token_seq, positions, (float*)out, num_tokens,

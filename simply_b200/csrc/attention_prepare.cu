@@ -157,11 +157,23 @@ pool_blocks_kernel(const T* __restrict__ cache, const int* __restrict__ block_ta
     const size_t base = is_key ? 0 : (size_t)G * page_size * d;
     float sum = 0.f;
     bool ok = true;
-    for (int j = 0; j < P; ++j) {
-      const long long p = first + j;
-      const long long page = block_table[(size_t)b * max_pages + p / page_size];
-      if (page < 0 || page >= num_pages) { ok = false; break; }
-      sum += to_f32<T>(cache[page * page_stride + base + ((size_t)m * page_size + p % page_size) * width + cc]);
+    for (int j0 = 0; j0 < P; j0 += 8) {  // eight tokens' loads together, added in the tokens' order
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        x[u] = 0.f;
+        if (j0 + u < P) {
+          const long long p = first + j0 + u;
+          const long long page = block_table[(size_t)b * max_pages + p / page_size];
+          if (page < 0 || page >= num_pages)
+            ok = false;
+          else
+            x[u] = to_f32<T>(cache[page * page_stride + base + ((size_t)m * page_size + p % page_size) * width + cc]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (j0 + u < P) sum += x[u];
     }
     if (!ok) {
       atomicOr(err, SB_ERR_BAD_PAGE);

@@ -166,7 +166,10 @@ __device__ __forceinline__ void scan_copy16(float* smem, const float* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
 }
 
-template <int RS>
+// VEC (head_dim a multiple of 4): a thread's rows are the groups of four 4 (rs + RS r) .. + 3, read
+// from shared memory as float4, with one partial sum per row of a group, so that a token's two
+// sums are four chains of eight instead of one of thirty-two.
+template <int RS, bool VEC>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ decay, const float* __restrict__ beta, float* __restrict__ state,
@@ -227,7 +230,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   float s[SCAN_ROWS];
 #pragma unroll
   for (int r = 0; r < SCAN_ROWS; ++r) {
-    const int row = rs + RS * r;
+    const int row = VEC ? 4 * (rs + RS * (r >> 2)) + (r & 3) : rs + RS * r;
     s[r] = (on && row < d) ? S[(size_t)row * dv + col] : 0.f;
   }
   int which = 0;
@@ -247,25 +250,58 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
       const float* gg = buf + (2 * SCAN_CHUNK + i) * d;
       const float vv = buf[3 * SCAN_CHUNK * d + i * cols_pad + min(col_local, cols - 1)];
       const float bb = buf[3 * SCAN_CHUNK * d + SCAN_CHUNK * cols_pad + i];
-      float dot = 0.f;
+      float dot = 0.f, od = 0.f;
+      if constexpr (VEC) {
+        float4 k4[SCAN_ROWS / 4];
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < SCAN_ROWS; ++r) {
-        const int row = rs + RS * r;
-        if (row < d) {
-          s[r] *= gg[row];
-          dot = fmaf(s[r], kk[row], dot);
+        for (int r = 0; r < SCAN_ROWS / 4; ++r) {
+          const int at = rs + RS * r;
+          if (4 * at < d) {
+            const float4 g4 = reinterpret_cast<const float4*>(gg)[at];
+            k4[r] = reinterpret_cast<const float4*>(kk)[at];
+            s[4 * r] *= g4.x; d0 = fmaf(s[4 * r], k4[r].x, d0);
+            s[4 * r + 1] *= g4.y; d1 = fmaf(s[4 * r + 1], k4[r].y, d1);
+            s[4 * r + 2] *= g4.z; d2 = fmaf(s[4 * r + 2], k4[r].z, d2);
+            s[4 * r + 3] *= g4.w; d3 = fmaf(s[4 * r + 3], k4[r].w, d3);
+          }
         }
-      }
+        dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
-      for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = bb * (vv - dot);
-      float od = 0.f;
+        for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float u = bb * (vv - dot);
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < SCAN_ROWS; ++r) {
-        const int row = rs + RS * r;
-        if (row < d) {
-          s[r] = fmaf(kk[row], u, s[r]);
-          od = fmaf(s[r], qq[row], od);
+        for (int r = 0; r < SCAN_ROWS / 4; ++r) {
+          const int at = rs + RS * r;
+          if (4 * at < d) {
+            const float4 q4 = reinterpret_cast<const float4*>(qq)[at];
+            s[4 * r] = fmaf(k4[r].x, u, s[4 * r]); o0 = fmaf(s[4 * r], q4.x, o0);
+            s[4 * r + 1] = fmaf(k4[r].y, u, s[4 * r + 1]); o1 = fmaf(s[4 * r + 1], q4.y, o1);
+            s[4 * r + 2] = fmaf(k4[r].z, u, s[4 * r + 2]); o2 = fmaf(s[4 * r + 2], q4.z, o2);
+            s[4 * r + 3] = fmaf(k4[r].w, u, s[4 * r + 3]); o3 = fmaf(s[4 * r + 3], q4.w, o3);
+          }
+        }
+        od = (o0 + o1) + (o2 + o3);
+      } else {
+#pragma unroll
+        for (int r = 0; r < SCAN_ROWS; ++r) {
+          const int row = rs + RS * r;
+          if (row < d) {
+            s[r] *= gg[row];
+            dot = fmaf(s[r], kk[row], dot);
+          }
+        }
+#pragma unroll
+        for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float u = bb * (vv - dot);
+#pragma unroll
+        for (int r = 0; r < SCAN_ROWS; ++r) {
+          const int row = rs + RS * r;
+          if (row < d) {
+            s[r] = fmaf(kk[row], u, s[r]);
+            od = fmaf(s[r], qq[row], od);
+          }
         }
       }
 #pragma unroll
@@ -277,7 +313,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   if (on && first_row_of_slot(slots, b)) {
 #pragma unroll
     for (int r = 0; r < SCAN_ROWS; ++r) {
-      const int row = rs + RS * r;
+      const int row = VEC ? 4 * (rs + RS * (r >> 2)) + (r & 3) : rs + RS * r;
       if (row < d) S[(size_t)row * dv + col] = s[r];
     }
   }
@@ -300,12 +336,18 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
   const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
   const size_t smem = (size_t)2 * SCAN_CHUNK * (3 * d + ((cols + 3) & ~3) + 4) * sizeof(float);
   if (smem > 200 * 1024) return -13;
-#define SB_SCAN(RS_)                                                                                          \
+#define SB_SCAN_V(RS_, VEC_)                                                                                  \
   do {                                                                                                        \
     if (smem > 48 * 1024)                                                                                     \
-      cudaFuncSetAttribute(delta_scan_kernel<RS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-    sb_launch(delta_scan_kernel<RS_>, grid, block, smem, stream, q, k, v, decay, beta, state, cu_q, slots,   \
-              num_slots, G, H, d, dv, cols, out, err);                                                        \
+      cudaFuncSetAttribute(delta_scan_kernel<RS_, VEC_>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                           (int)smem);                                                                        \
+    sb_launch(delta_scan_kernel<RS_, VEC_>, grid, block, smem, stream, q, k, v, decay, beta, state, cu_q,    \
+              slots, num_slots, G, H, d, dv, cols, out, err);                                                 \
+  } while (0)
+#define SB_SCAN(RS_)                    \
+  do {                                  \
+    if (d % 4 == 0) SB_SCAN_V(RS_, true); \
+    else SB_SCAN_V(RS_, false);         \
   } while (0)
   switch (rs) {
     case 1: SB_SCAN(1); break;
@@ -316,6 +358,7 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
     default: SB_SCAN(32); break;
   }
 #undef SB_SCAN
+#undef SB_SCAN_V
   SB_LAUNCH_CHECK();
   return 0;
 }
