@@ -151,8 +151,13 @@ extern "C" int sb_delta_inputs(const void* pre, int pre_width, const void* low, 
 // ---------------------------------------------------------------------------
 // The scan.  A block owns `cols` value columns of one (sequence, head) and walks the sequence's
 // tokens of this step in order.  A column of S is held by RS neighbouring lanes, each with the
-// rows rs, rs + RS, ... (at most 32) in registers; the two sums over rows per token are
-// butterfly sums over those lanes, in an order that does not depend on the step's shape.  k, q,
+// rows rs, rs + RS, ... (ROWS of them) in registers; the two sums over rows per token are
+// butterfly sums over those lanes, in an order that does not depend on the step's shape.  A
+// token is a chain of dependent instructions, and a sequence has only heads * value_dim columns to
+// work on side by side: few rows per thread (8, a column over up to 32 lanes) keep the chain
+// short and give the SMs several warps each, which is what the walk's time hangs on (with 32 rows
+// per thread a 2,048-token prompt took 1 microsecond per token, one warp per scheduler, every
+// instruction's latency in the open).  k, q,
 // g, v and beta of SCAN_CHUNK tokens at a time come to shared memory by cp.async, the next
 // chunk while the block works on this one.
 // ---------------------------------------------------------------------------
@@ -169,7 +174,7 @@ __device__ __forceinline__ void scan_copy16(float* smem, const float* gmem) {
 // VEC (head_dim a multiple of 4): a thread's rows are the groups of four 4 (rs + RS r) .. + 3, read
 // from shared memory as float4, with one partial sum per row of a group, so that a token's two
 // sums are four chains of eight instead of one of thirty-two.
-template <int RS, bool VEC>
+template <int RS, int ROWS, bool VEC>
 __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ decay, const float* __restrict__ beta, float* __restrict__ state,
@@ -193,11 +198,24 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   const int cols_pad = (cols + 3) & ~3;
   const int buffer = SCAN_CHUNK * (3 * d + cols_pad + 4);
   const bool vec = (d & 3) == 0;
+  // When a row's 16-byte pieces divide the block: a fixed piece per thread, rows dealt out in turn.
+  const int pieces = d >> 2;
+  const int copy_rows = (vec && pieces <= (int)blockDim.x && blockDim.x % pieces == 0) ? blockDim.x / pieces : 0;
+  const int copy_row = copy_rows ? threadIdx.x / pieces : 0, copy_c = copy_rows ? (threadIdx.x % pieces) * 4 : 0;
 
   auto issue = [&](int which, int base) {
     float* buf = stage + which * buffer;
     const int count = min(SCAN_CHUNK, n - base);
-    if (vec) {
+    if (vec && copy_rows > 0) {
+      // thread (copy_row, copy_c) of every pass copies 16 bytes of one of the chunk's 3 * count rows
+      for (int row = copy_row; row < 3 * count; row += copy_rows) {
+        const int i = row / 3, kind = row - 3 * i;
+        const size_t t = (size_t)(first + base + i);
+        const float* src = kind == 0 ? k + (t * G + g_head) * d : kind == 1 ? q + (t * G + g_head) * d
+                                                                             : decay + (t * H + h) * d;
+        scan_copy16(buf + (kind * SCAN_CHUNK + i) * d + copy_c, src + copy_c);
+      }
+    } else if (vec) {
       const int d4 = d >> 2;
       for (int idx = threadIdx.x; idx < count * 3 * d4; idx += blockDim.x) {
         const int i = idx / (3 * d4), rem = idx - i * 3 * d4, kind = rem / d4, c = (rem - kind * d4) * 4;
@@ -227,9 +245,9 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 
   if (n > 0) issue(0, 0);
   float* S = state + ((size_t)slot * H + h) * d * dv;
-  float s[SCAN_ROWS];
+  float s[ROWS];
 #pragma unroll
-  for (int r = 0; r < SCAN_ROWS; ++r) {
+  for (int r = 0; r < ROWS; ++r) {
     const int row = VEC ? 4 * (rs + RS * (r >> 2)) + (r & 3) : rs + RS * r;
     s[r] = (on && row < d) ? S[(size_t)row * dv + col] : 0.f;
   }
@@ -252,10 +270,10 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
       const float bb = buf[3 * SCAN_CHUNK * d + SCAN_CHUNK * cols_pad + i];
       float dot = 0.f, od = 0.f;
       if constexpr (VEC) {
-        float4 k4[SCAN_ROWS / 4];
+        float4 k4[ROWS / 4];
         float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-        for (int r = 0; r < SCAN_ROWS / 4; ++r) {
+        for (int r = 0; r < ROWS / 4; ++r) {
           const int at = rs + RS * r;
           if (4 * at < d) {
             const float4 g4 = reinterpret_cast<const float4*>(gg)[at];
@@ -272,7 +290,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         const float u = bb * (vv - dot);
         float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-        for (int r = 0; r < SCAN_ROWS / 4; ++r) {
+        for (int r = 0; r < ROWS / 4; ++r) {
           const int at = rs + RS * r;
           if (4 * at < d) {
             const float4 q4 = reinterpret_cast<const float4*>(qq)[at];
@@ -285,7 +303,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         od = (o0 + o1) + (o2 + o3);
       } else {
 #pragma unroll
-        for (int r = 0; r < SCAN_ROWS; ++r) {
+        for (int r = 0; r < ROWS; ++r) {
           const int row = rs + RS * r;
           if (row < d) {
             s[r] *= gg[row];
@@ -296,7 +314,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
         for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
         const float u = bb * (vv - dot);
 #pragma unroll
-        for (int r = 0; r < SCAN_ROWS; ++r) {
+        for (int r = 0; r < ROWS; ++r) {
           const int row = rs + RS * r;
           if (row < d) {
             s[r] = fmaf(kk[row], u, s[r]);
@@ -312,7 +330,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
   }
   if (on && first_row_of_slot(slots, b)) {
 #pragma unroll
-    for (int r = 0; r < SCAN_ROWS; ++r) {
+    for (int r = 0; r < ROWS; ++r) {
       const int row = VEC ? 4 * (rs + RS * (r >> 2)) + (r & 3) : rs + RS * r;
       if (row < d) S[(size_t)row * dv + col] = s[r];
     }
@@ -324,30 +342,34 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
                              int H, int d, int dv, float* out, int* err, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (d <= 0 || d > 32 * SCAN_ROWS || dv <= 0 || G <= 0 || H % G) return -13;
+  // Rows per thread: 8 where the head allows (a column over at most 32 lanes), else 32.
+  const bool vec = d % 4 == 0;
+  const int rows = (vec && d <= 8 * 32) ? 8 : SCAN_ROWS;
   int rs = 1;
-  while (rs * SCAN_ROWS < d) rs <<= 1;
+  while (rs * rows < d) rs <<= 1;
   const int threads = 128;
   int cols = threads / rs;
   if (cols > dv) cols = dv;
   // Few (sequence, head) pairs: narrower blocks, so that more SMs share the columns (not below
   // 64 threads: a block's threads also fetch its chunks).
-  while (cols * rs > 64 && (long long)num_seqs * H * ((dv + cols - 1) / cols) < 148) cols = (cols + 1) / 2;
+  while (cols * rs > 64 && (long long)num_seqs * H * ((dv + cols - 1) / cols) < 2 * 148) cols = (cols + 1) / 2;
   const int block = ((cols * rs + 31) / 32) * 32;
   const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
   const size_t smem = (size_t)2 * SCAN_CHUNK * (3 * d + ((cols + 3) & ~3) + 4) * sizeof(float);
   if (smem > 200 * 1024) return -13;
-#define SB_SCAN_V(RS_, VEC_)                                                                                  \
+#define SB_SCAN_V(RS_, ROWS_, VEC_)                                                                           \
   do {                                                                                                        \
     if (smem > 48 * 1024)                                                                                     \
-      cudaFuncSetAttribute(delta_scan_kernel<RS_, VEC_>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+      cudaFuncSetAttribute(delta_scan_kernel<RS_, ROWS_, VEC_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                                        \
-    sb_launch(delta_scan_kernel<RS_, VEC_>, grid, block, smem, stream, q, k, v, decay, beta, state, cu_q,    \
-              slots, num_slots, G, H, d, dv, cols, out, err);                                                 \
+    sb_launch(delta_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, q, k, v, decay, beta, state,   \
+              cu_q, slots, num_slots, G, H, d, dv, cols, out, err);                                           \
   } while (0)
-#define SB_SCAN(RS_)                    \
-  do {                                  \
-    if (d % 4 == 0) SB_SCAN_V(RS_, true); \
-    else SB_SCAN_V(RS_, false);         \
+#define SB_SCAN(RS_)                                  \
+  do {                                                \
+    if (rows == 8) SB_SCAN_V(RS_, 8, true);           \
+    else if (vec) SB_SCAN_V(RS_, SCAN_ROWS, true);    \
+    else SB_SCAN_V(RS_, SCAN_ROWS, false);            \
   } while (0)
   switch (rs) {
     case 1: SB_SCAN(1); break;
