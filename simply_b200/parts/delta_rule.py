@@ -111,7 +111,7 @@ class GatedDeltaRule(Mixer):
     out = a2.new_zeros(a2.shape[0] + g2.shape[0], self.rank_weight.shape[0])
     out[:a2.shape[0], :ra] = a2
     out[a2.shape[0]:, ra:ra + rg] = g2
-    self.out_weight = out.contiguous()
+    self.out_weight = _pad_rows(out)
     self.o_proj.bind(tensors)
     conv = [t[f"{p.name}.{self.names['conv']}"] for p in (self.q_proj, self.k_proj, self.v_proj)]
     self.conv_weight = torch.cat([c.float() for c in conv], dim=0).contiguous()

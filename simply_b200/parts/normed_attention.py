@@ -117,9 +117,12 @@ class QKNormAttention(Mixer):
     return specs + [self.o_proj.spec()]
 
   def bind(self, tensors, ops) -> None:
-    ops.check_attention(self.head_dim, self.num_heads, self.num_kv_heads)
+    if self.head_dim % 2 == 0:  # (odd head sizes run on the general kernel, which takes any)
+      ops.check_attention(self.head_dim, self.num_heads, self.num_kv_heads)
     names = [self.q_proj.name] + ([self.k_proj.name, self.v_proj.name] if self.project_kv else [])
-    self.qkv_weight = fuse_rows([tensors[n] for n in names])
+    qkv = fuse_rows([tensors[n] for n in names])
+    extra = -qkv.shape[0] % 8  # whole 16-byte groups of output features for the products' stores
+    self.qkv_weight = torch.cat([qkv, qkv.new_zeros(extra, qkv.shape[1])]).contiguous() if extra else qkv
     self.o_proj.bind(tensors)
     self.q_norm = tensors[self.q_norm_name].float().contiguous()
     self.k_norm = tensors[self.k_norm_name].float().contiguous() if self.project_kv else None
