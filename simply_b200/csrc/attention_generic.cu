@@ -81,14 +81,15 @@ __device__ __forceinline__ void gen_tile(const KT* kr, const KT* vr, const float
 #pragma unroll
   for (int i = 0; i < GEN_MAX_DPL; ++i) acc[i] *= alpha;
   const unsigned valid_mask = __ballot_sync(0xffffffffu, valid);
-  // Four keys at a time: their values are fetched together, then added in the keys' order.
-  for (int j0 = 0; j0 < 32; j0 += 4) {
-    const unsigned four = (valid_mask >> j0) & 0xfu;  // uniform over the warp
+  // Eight keys at a time: their values are fetched together, then added in the keys' order.
+  constexpr int KEYS = 8;
+  for (int j0 = 0; j0 < 32; j0 += KEYS) {
+    const unsigned four = (valid_mask >> j0) & ((1u << KEYS) - 1u);  // uniform over the warp
     if (!four) continue;
-    float pj[4];
-    const KT* vj[4];
+    float pj[KEYS];
+    const KT* vj[KEYS];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < KEYS; ++u) {
       pj[u] = __shfl_sync(0xffffffffu, p, j0 + u);
       vj[u] = reinterpret_cast<const KT*>(__shfl_sync(0xffffffffu, (unsigned long long)vr, j0 + u));
     }
@@ -96,11 +97,11 @@ __device__ __forceinline__ void gen_tile(const KT* kr, const KT* vr, const float
     for (int i = 0; i < GEN_MAX_DPL; ++i) {
       const int d = lane + 32 * i;
       if (d < v_dim) {
-        float x[4];
+        float x[KEYS];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) x[u] = ((four >> u) & 1u) ? to_f32<KT>(vj[u][d]) : 0.f;
+        for (int u = 0; u < KEYS; ++u) x[u] = ((four >> u) & 1u) ? to_f32<KT>(vj[u][d]) : 0.f;
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < KEYS; ++u)
           if ((four >> u) & 1u) acc[i] = fmaf(pj[u], x[u], acc[i]);
       }
     }

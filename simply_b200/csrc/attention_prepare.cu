@@ -24,12 +24,20 @@ qk_norm_rotate_store_kernel(const T* __restrict__ qkv, int row_width, const floa
                             int H, int G, int d, int dv, int page_size, int num_pages, int write_cache, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
-  extern __shared__ float row[];  // (H + G) d floats + 33 scratch
+  extern __shared__ float row[];  // (H + G) d floats, 33 scratch, cos and sin of rot_dims / 2 and of dv / 2 angles
   const int nq = H * d, nk = G * d;
   float* scratch = row + nq + nk;
+  const int half = rot_dims / 2, vhalf = dv / 2;
+  float* cs_qk = scratch + 33;    // [half] cos, [half] sin
+  float* cs_v = cs_qk + 2 * half;  // [vhalf] cos, [vhalf] sin
   const int t = blockIdx.x;
   const T* x = qkv + (size_t)t * row_width;
   const float pos = (float)positions[t];
+  // A token's angles are the same for all its heads: once per block.
+  if (rot_freq != nullptr)
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * rot_freq[i], cs_qk + half + i, cs_qk + i);
+  if (value_freq != nullptr && write_cache && nk > 0)
+    for (int i = threadIdx.x; i < vhalf; i += blockDim.x) sincosf(pos * value_freq[i], cs_v + vhalf + i, cs_v + i);
 
   float ssq = 0.f, ssk = 0.f;
   for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
@@ -60,14 +68,12 @@ qk_norm_rotate_store_kernel(const T* __restrict__ qkv, int row_width, const floa
     }
   }
   const size_t page_stride = (size_t)G * page_size * (d + dv);
-  const int half = rot_dims / 2;
   for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
     const int head = i / d, c = i % d;
     float v = row[i];
     if (rot_freq != nullptr && c < rot_dims) {
       const int pair = c < half ? c : c - half;
-      float sn, cs;
-      sincosf(pos * rot_freq[pair], &sn, &cs);
+      const float cs = cs_qk[pair], sn = cs_qk[half + pair];
       const float a = row[i - c + pair], b = row[i - c + pair + half];
       v = c < half ? a * cs - b * sn : b * cs + a * sn;
     }
@@ -81,14 +87,12 @@ qk_norm_rotate_store_kernel(const T* __restrict__ qkv, int row_width, const floa
   if (page >= 0) {
     const T* vx = x + nq + nk;
     T* dst = cache + page * page_stride + (size_t)G * page_size * d;
-    const int vhalf = dv / 2;
     for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
       const int m = i / dv, c = i % dv;
       float v = to_f32<T>(vx[i]);
       if (value_freq != nullptr) {
         const int pair = c < vhalf ? c : c - vhalf;
-        float sn, cs;
-        sincosf(pos * value_freq[pair], &sn, &cs);
+        const float cs = cs_v[pair], sn = cs_v[vhalf + pair];
         const float a = to_f32<T>(vx[i - c + pair]), b = to_f32<T>(vx[i - c + pair + vhalf]);
         v = c < vhalf ? a * cs - b * sn : b * cs + a * sn;
       }
@@ -105,7 +109,7 @@ extern "C" int sb_qk_norm_rotate_store(const void* qkv, int row_width, int dtype
                                        int page_size, int num_pages, int write_cache, int* err,
                                        cudaStream_t stream) {
   if (num_tokens == 0) return 0;
-  const size_t smem = ((size_t)(H + G) * d + 33) * sizeof(float);
+  const size_t smem = ((size_t)(H + G) * d + 33 + rot_dims + dv) * sizeof(float);
   if (smem > 200 * 1024) return -2;
   if (rot_dims % 2 || rot_dims > d || (value_freq != nullptr && dv % 2)) return -4;
   if (dtype == SB_DTYPE_F32) {
@@ -129,7 +133,7 @@ extern "C" int sb_qk_norm_rotate_store(const void* qkv, int row_width, int dtype
 // into the storage of block entries.  Grid (block within the step, sequence, kv head).
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(1024)
 pool_blocks_kernel(const T* __restrict__ cache, const int* __restrict__ block_table, int max_pages, int num_pages,
                    T* __restrict__ pool, const int* __restrict__ pool_table, int pool_max_pages,
                    int pool_pages, const int* __restrict__ cu_q, const int* __restrict__ q_start, int G, int d,
@@ -140,7 +144,7 @@ pool_blocks_kernel(const T* __restrict__ cache, const int* __restrict__ block_ta
   const int start = q_start[b], end = start + cu_q[b + 1] - cu_q[b];
   const int c = start / P + blockIdx.x;
   if (c >= end / P) return;
-  const long long first = (long long)c * P;
+  const int first = c * P;
   const int entries = (page_size + P - 1) / P;
   const long long to = pool_table[(size_t)b * pool_max_pages + first / page_size];
   if (to < 0 || to >= pool_pages) {
@@ -150,37 +154,56 @@ pool_blocks_kernel(const T* __restrict__ cache, const int* __restrict__ block_ta
   const size_t page_stride = (size_t)G * page_size * (d + dv);
   const size_t pool_stride = (size_t)G * entries * (d + dv);
   const size_t entry = (size_t)m * entries + (first % page_size) / P;
-  for (int ch = threadIdx.x; ch < d + dv; ch += blockDim.x) {
-    const bool is_key = ch < d;
-    const int cc = is_key ? ch : ch - d;
-    const int width = is_key ? d : dv;
-    const size_t base = is_key ? 0 : (size_t)G * page_size * d;
-    float sum = 0.f;
-    bool ok = true;
-    for (int j0 = 0; j0 < P; j0 += 8) {  // eight tokens' loads together, added in the tokens' order
-      float x[8];
+  // Where the block's tokens live: worked out once per 64 tokens, by the first threads.
+  __shared__ long long where[64];  // the token's page times the page's size; -1: not held
+  __shared__ int row_in_page[64];
+  float sums[4] = {0.f, 0.f, 0.f, 0.f};  // this thread's channels: threadIdx.x, + 128, ...
+  bool ok = true;
+  for (int j0 = 0; j0 < P; j0 += 64) {
+    const int count = min(64, P - j0);
+    __syncthreads();
+    if ((int)threadIdx.x < count) {
+      const int p = first + j0 + threadIdx.x;
+      const long long page = block_table[(size_t)b * max_pages + p / page_size];
+      where[threadIdx.x] = (page < 0 || page >= num_pages) ? -1 : page * (long long)page_stride;
+      row_in_page[threadIdx.x] = p % page_size;
+    }
+    __syncthreads();
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        x[u] = 0.f;
-        if (j0 + u < P) {
-          const long long p = first + j0 + u;
-          const long long page = block_table[(size_t)b * max_pages + p / page_size];
-          if (page < 0 || page >= num_pages)
-            ok = false;
-          else
-            x[u] = to_f32<T>(cache[page * page_stride + base + ((size_t)m * page_size + p % page_size) * width + cc]);
+    for (int turn = 0; turn < 4; ++turn) {
+      const int ch = turn * blockDim.x + threadIdx.x;
+      if (ch >= d + dv) break;
+      const bool is_key = ch < d;
+      const int cc = is_key ? ch : ch - d, width = is_key ? d : dv;
+      const size_t base = (is_key ? 0 : (size_t)G * page_size * d) + (size_t)m * page_size * width + cc;
+      float sum = sums[turn];
+      for (int j = 0; j < count; j += 8) {  // eight tokens' loads together, added in the tokens' order
+        float x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          x[u] = 0.f;
+          if (j + u < count) {
+            const long long at = where[j + u];
+            if (at < 0) ok = false;
+            else x[u] = to_f32<T>(cache[at + base + (size_t)row_in_page[j + u] * width]);
+          }
         }
-      }
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        if (j0 + u < P) sum += x[u];
+        for (int u = 0; u < 8; ++u)
+          if (j + u < count) sum += x[u];
+      }
+      sums[turn] = sum;
     }
-    if (!ok) {
-      atomicOr(err, SB_ERR_BAD_PAGE);
-      continue;
-    }
+  }
+  if (!ok) atomicOr(err, SB_ERR_BAD_PAGE);
+#pragma unroll
+  for (int turn = 0; turn < 4; ++turn) {
+    const int ch = turn * blockDim.x + threadIdx.x;
+    if (ch >= d + dv || !ok) break;
+    const bool is_key = ch < d;
+    const int cc = is_key ? ch : ch - d, width = is_key ? d : dv;
     T* dst = pool + to * pool_stride + (is_key ? 0 : (size_t)G * entries * d) + entry * width + cc;
-    *dst = from_f32<T>(sum / (float)P);
+    *dst = from_f32<T>(sums[turn] / (float)P);
   }
 }
 
@@ -191,11 +214,15 @@ extern "C" int sb_pool_blocks(const void* cache, int dtype, const int* block_tab
   if (num_seqs == 0 || max_blocks <= 0) return 0;
   if (P <= 0) return -13;
   const dim3 grid(max_blocks, num_seqs, G);
+  // a thread keeps up to four channels' sums: wider heads get wider blocks
+  int threads = 128;
+  while (threads * 4 < d + dv && threads < 1024) threads *= 2;
+  if (threads * 4 < d + dv) return -13;
   if (dtype == SB_DTYPE_F32)
-    sb_launch(pool_blocks_kernel<float>, grid, 128, 0, stream, (const float*)cache, block_table, max_pages,
+    sb_launch(pool_blocks_kernel<float>, grid, threads, 0, stream, (const float*)cache, block_table, max_pages,
               num_pages, (float*)pool, pool_table, pool_max_pages, pool_pages, cu_q, q_start, G, d, dv, page_size, P, err);
   else
-    sb_launch(pool_blocks_kernel<bf16>, grid, 128, 0, stream, (const bf16*)cache, block_table, max_pages,
+    sb_launch(pool_blocks_kernel<bf16>, grid, threads, 0, stream, (const bf16*)cache, block_table, max_pages,
               num_pages, (bf16*)pool, pool_table, pool_max_pages, pool_pages, cu_q, q_start, G, d, dv, page_size, P, err);
   SB_LAUNCH_CHECK();
   return 0;
