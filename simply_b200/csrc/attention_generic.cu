@@ -81,8 +81,9 @@ __device__ __forceinline__ void gen_tile(const KT* kr, const KT* vr, const float
 #pragma unroll
   for (int i = 0; i < GEN_MAX_DPL; ++i) acc[i] *= alpha;
   const unsigned valid_mask = __ballot_sync(0xffffffffu, valid);
-  // Eight keys at a time: their values are fetched together, then added in the keys' order.
-  constexpr int KEYS = 8;
+  // Four keys at a time: their values are fetched together, then added in the keys' order (eight
+  // at a time cost registers and were slower).
+  constexpr int KEYS = 4;
   for (int j0 = 0; j0 < 32; j0 += KEYS) {
     const unsigned four = (valid_mask >> j0) & ((1u << KEYS) - 1u);  // uniform over the warp
     if (!four) continue;

@@ -39,11 +39,27 @@ qk_norm_rotate_store_kernel(const T* __restrict__ qkv, int row_width, const floa
   if (value_freq != nullptr && write_cache && nk > 0)
     for (int i = threadIdx.x; i < vhalf; i += blockDim.x) sincosf(pos * value_freq[i], cs_v + vhalf + i, cs_v + i);
 
+  constexpr int N = Vec<T>::N;
+  const bool vec = d % N == 0 && row_width % N == 0;  // whole 16-byte groups inside a head
   float ssq = 0.f, ssk = 0.f;
-  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
-    const float v = to_f32<T>(x[i]);
-    row[i] = v;
-    if (i < nq) ssq = fmaf(v, v, ssq); else ssk = fmaf(v, v, ssk);
+  if (vec) {
+    for (int i = threadIdx.x * N; i < nq + nk; i += blockDim.x * N) {
+      float v[N];
+      Vec<T>::load(x + i, v);
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        row[i + e] = v[e];
+        ss = fmaf(v[e], v[e], ss);
+      }
+      if (i < nq) ssq += ss; else ssk += ss;
+    }
+  } else {
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+      const float v = to_f32<T>(x[i]);
+      row[i] = v;
+      if (i < nq) ssq = fmaf(v, v, ssq); else ssk = fmaf(v, v, ssk);
+    }
   }
   ssq = block_sum(ssq, scratch);
   const float rq = 1.0f / sqrtf(ssq / (float)nq + eps);
@@ -68,7 +84,30 @@ qk_norm_rotate_store_kernel(const T* __restrict__ qkv, int row_width, const floa
     }
   }
   const size_t page_stride = (size_t)G * page_size * (d + dv);
-  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+  if (vec) {
+    for (int i0 = threadIdx.x * N; i0 < nq + nk; i0 += blockDim.x * N) {
+      const int head = i0 / d, c0 = i0 - head * d;
+      const float scale = i0 < nq ? head_scale[head] : 1.f;
+      float o[N];
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        const int c = c0 + e;
+        float v = row[i0 + e];
+        if (rot_freq != nullptr && c < rot_dims) {
+          const int pair = c < half ? c : c - half;
+          const float cs = cs_qk[pair], sn = cs_qk[half + pair];
+          const float a = row[i0 - c0 + pair], b = row[i0 - c0 + pair + half];
+          v = c < half ? a * cs - b * sn : b * cs + a * sn;
+        }
+        o[e] = v * scale;
+      }
+      if (i0 < nq)
+        Vec<T>::store(q_out + (size_t)t * nq + i0, o);
+      else if (page >= 0)
+        Vec<T>::store(cache + page * page_stride + ((size_t)(head - H) * page_size + off) * d + c0, o);
+    }
+  }
+  for (int i = threadIdx.x; i < (vec ? 0 : nq + nk); i += blockDim.x) {
     const int head = i / d, c = i % d;
     float v = row[i];
     if (rot_freq != nullptr && c < rot_dims) {
@@ -87,7 +126,28 @@ qk_norm_rotate_store_kernel(const T* __restrict__ qkv, int row_width, const floa
   if (page >= 0) {
     const T* vx = x + nq + nk;
     T* dst = cache + page * page_stride + (size_t)G * page_size * d;
-    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+    const bool vec_v = vec && dv % N == 0 && (value_freq == nullptr || vhalf % N == 0) && (nq + nk) % N == 0;
+    if (vec_v) {
+      for (int i0 = threadIdx.x * N; i0 < G * dv; i0 += blockDim.x * N) {
+        const int m = i0 / dv, c0 = i0 - m * dv;
+        float own[N], other[N], o[N];
+        Vec<T>::load(vx + i0, own);
+        if (value_freq != nullptr) {
+          Vec<T>::load(vx + (c0 < vhalf ? i0 + vhalf : i0 - vhalf), other);
+#pragma unroll
+          for (int e = 0; e < N; ++e) {
+            const int pair = c0 < vhalf ? c0 + e : c0 + e - vhalf;
+            const float cs = cs_v[pair], sn = cs_v[vhalf + pair];
+            o[e] = c0 < vhalf ? own[e] * cs - other[e] * sn : own[e] * cs + other[e] * sn;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < N; ++e) o[e] = own[e];
+        }
+        Vec<T>::store(dst + ((size_t)m * page_size + off) * dv + c0, o);
+      }
+    }
+    for (int i = threadIdx.x; i < (vec_v ? 0 : G * dv); i += blockDim.x) {
       const int m = i / dv, c = i % dv;
       float v = to_f32<T>(vx[i]);
       if (value_freq != nullptr) {

@@ -438,18 +438,48 @@ normed_mean_kernel(MeanBranches br, int count, float eps, int width, T* __restri
   pdl_launch_dependents();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
+  constexpr int N = Vec<T>::N;
+  const bool vec = width % N == 0;
   float rstd[4];
   for (int i = 0; i < count; ++i) {
     const T* x = reinterpret_cast<const T*>(br.x[i]) + (size_t)t * width;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      const float a = to_f32<T>(x[c]);
-      ss = fmaf(a, a, ss);
+    if (vec) {
+      for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {
+        float a[N];
+        Vec<T>::load(x + c, a);
+#pragma unroll
+        for (int e = 0; e < N; ++e) ss = fmaf(a[e], a[e], ss);
+      }
+    } else {
+      for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float a = to_f32<T>(x[c]);
+        ss = fmaf(a, a, ss);
+      }
     }
     ss = block_sum(ss, scratch);
     rstd[i] = 1.0f / sqrtf(ss / (float)width + eps);
   }
   const float share = 1.0f / (float)count;
+  if (vec) {
+    for (int c = threadIdx.x * N; c < width; c += blockDim.x * N) {
+      float acc[N];
+#pragma unroll
+      for (int e = 0; e < N; ++e) acc[e] = 0.f;
+      for (int i = 0; i < count; ++i) {
+        float a[N], w[N];
+        Vec<T>::load(reinterpret_cast<const T*>(br.x[i]) + (size_t)t * width + c, a);
+#pragma unroll
+        for (int e = 0; e < N; e += 4) Vec<float>::load(br.w[i] + c + e, w + e);
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[e] += a[e] * rstd[i] * w[e];
+      }
+#pragma unroll
+      for (int e = 0; e < N; ++e) acc[e] *= share;
+      Vec<T>::store(out + (size_t)t * width + c, acc);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float acc = 0.f;
     for (int i = 0; i < count; ++i)
