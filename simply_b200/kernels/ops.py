@@ -115,6 +115,23 @@ class AttentionGraphPlan:
     return CudaOps.decode_chunk_range(lengths, steps, self.window, self.chunk)
 
 
+class PooledAttentionGraphPlan:
+  """Static work list for attention with pooled blocks in a decode graph: every request brings one
+  token and is one tile of the prefill kernel, so the list is (request, 0) for each and never changes."""
+
+  def __init__(self, key: tuple, batch: int):
+    self.key, self.batch, self.words = key, batch, 2 * batch
+
+  def bind(self, view: torch.Tensor) -> dict:
+    return dict(num_prefill=self.batch, num_decode=0, rows_per_tile=64, prefill_items=view[:2 * self.batch])
+
+  def fill(self, host_words: np.ndarray, lengths: np.ndarray, steps: int) -> None:
+    host_words[:2 * self.batch] = np.stack([np.arange(self.batch), np.zeros(self.batch, dtype=np.int64)], axis=1).reshape(-1)
+
+  def ranges(self, lengths: np.ndarray, steps: int):
+    return ()
+
+
 class CudaOps:
 
   name = "cuda"
@@ -469,8 +486,17 @@ class CudaOps:
       return None
     return AttentionGraphPlan(self, window, group, num_kv_heads, head_dim, batch, bucket, max_burst, page_size)
 
+  def pooled_attention_graph_plan(self, *, window: int | None, num_heads: int, num_kv_heads: int, head_dim: int,
+                                  value_dim: int, pool: int, batch: int, page_size: int):
+    """The static work list a decode graph needs for a layer with pooled blocks, or None when the
+    general kernel serves it (which reads no list)."""
+    group = num_heads // num_kv_heads
+    if value_dim != head_dim or not window or not self._uses_tensor_core_attention(head_dim, group):
+      return None
+    return PooledAttentionGraphPlan(self._plan_key(window, group, num_kv_heads, head_dim, page_size) + ("pooled", pool), batch)
+
   def _attention_plan(self, ctx: Any, window: int | None, group: int, force_rows: int = 0,
-                      num_kv_heads: int = 1, head_dim: int = 0, tag: tuple = ()) -> dict:
+                      num_kv_heads: int = 1, head_dim: int = 0, tag: tuple = (), all_tiles: bool = False) -> dict:
     """Work lists of the two tensor-core kernels for this step, per kind of layer (`_plan_key`).
 
     Sequences with at most 16 query rows per kv head (one or a few new tokens) go to the
@@ -484,7 +510,7 @@ class CudaOps:
       return plan
     cu_q, q_start = ctx.host["cu_q"], ctx.host["q_start"].astype(np.int64)
     q_len = np.diff(cu_q).astype(np.int64)
-    small = q_len * group <= 16
+    small = (q_len * group <= 16) & (not all_tiles)  # all_tiles: the tile kernel takes every sequence
     # Tiles of 64 query rows (finer grains balance better over the SMs than tiles of 128).
     rows_per_tile = force_rows or self.prefill_rows or 64
     tokens_per_tile = rows_per_tile // group
@@ -772,16 +798,19 @@ class CudaOps:
                    num_kv_heads, head_dim, value_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
                    int(window or 0), *pool_args, _ptr(token_list), _ptr(self.err))
 
-      # Portions of prompts go to the tensor-core kernel (mma.sync tiles of 64 rows, the block
-      # entries in tiles of their own ahead of the tokens); sequences that bring a token or a few,
-      # and shapes that kernel does not take, to the general one.
-      tensor_cores = (value_dim == head_dim and q.dtype == torch.bfloat16 and window
-                      and self._uses_tensor_core_attention(head_dim, group) and ctx.max_q_len * group > 16
-                      and "cu_q" in ctx.host)
+      # bfloat16 with key size = value size: the tensor-core tile kernel (mma.sync tiles of 64 rows,
+      # the block entries in tiles of their own ahead of the tokens) for prompt portions and single
+      # tokens alike; other shapes and float32: the general kernel.
+      tensor_cores = (pooled is not None and value_dim == head_dim and q.dtype == torch.bfloat16 and window
+                      and self._uses_tensor_core_attention(head_dim, group))
       if not tensor_cores:
         general(None, t)
         return out
-      plan = self._attention_plan(ctx, window, group, 0, num_kv_heads, head_dim, tag=("pooled", pool_len))
+      key = self._plan_key(window, group, num_kv_heads, head_dim, ctx.page_size) + ("pooled", pool_len)
+      plan = ctx.memo.get(key)  # (a decode graph brings its static list)
+      if plan is None:
+        plan = self._attention_plan(ctx, window, group, 0, num_kv_heads, head_dim, tag=("pooled", pool_len),
+                                    all_tiles=True)
       if plan["num_prefill"]:
         rc = self._attention_lib(head_dim)[5](
             _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1], _ptr(ctx.cu_q), _ptr(ctx.q_start),
@@ -791,14 +820,6 @@ class CudaOps:
         self.launches += 1
         if rc:
           raise KernelError(f"sb_attn_prefill_pooled: {_STATUS.get(rc, rc)}")
-      if plan["num_decode"]:
-        rows = ctx.memo.get(("few_token_rows", group))
-        if rows is None:
-          cu_q = ctx.host["cu_q"]
-          few = [np.arange(cu_q[b], cu_q[b + 1]) for b in range(ctx.num_seqs) if (cu_q[b + 1] - cu_q[b]) * group <= 16]
-          rows = ctx.memo[("few_token_rows", group)] = torch.from_numpy(
-              np.concatenate(few).astype(np.int32)).to(self.device, non_blocking=True)
-        general(rows, rows.numel())
       return out
     if q.dtype == torch.bfloat16 and self._uses_tensor_core_attention(head_dim, group):
       prefill, decode, _, prefill_tc, prefill_pair = self._attention_lib(head_dim)[:5]

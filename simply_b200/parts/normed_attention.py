@@ -99,7 +99,12 @@ class QKNormAttention(Mixer):
                                           stride=self.pool)}
 
   def graph_plans(self, ops, batch: int, bucket: int, max_burst: int, page_size: int) -> list:
-    if self.pool is not None or self.value_dim != self.head_dim:
+    if self.pool is not None:
+      plan = ops.pooled_attention_graph_plan(
+          window=self.window, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+          value_dim=self.value_dim, pool=self.pool, batch=batch, page_size=page_size)
+      return [plan] if plan is not None else []
+    if self.value_dim != self.head_dim:
       return []
     plan = ops.attention_graph_plan(
         window=self.window, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,

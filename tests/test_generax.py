@@ -212,6 +212,29 @@ def test_bfloat16_generation_runs_and_samples():
   engine.ops.check_errors()
 
 
+@pytest.mark.gpu
+def test_bfloat16_single_tokens_replayed_from_cuda_graphs():
+  """Three requests side by side, their last 30 tokens one by one as replays of the decode graph of
+  four rows; the logits of every replayed step against the plain model."""
+  cfg_dict = gx.CONFIG_A
+  engine, t = engine_for(cfg_dict, ("bfloat16", "cuda"), seed=6, slots=4, graphs=True)
+  assert engine._decode_runner is not None
+  engine._decode_runner.keep_logits = True
+  w = gx.as_numpy(t)
+  requests = [tokens_for(cfg_dict, n, 50 + i) for i, n in enumerate((70, 41, 55))]
+  want = [plain.forward(cfg_dict, w, r) for r in requests]
+  slots = [engine.open_request() for _ in requests]
+  heads = [len(r) - 30 for r in requests]
+  engine.step_raw([StepEntry(s, r[:h], ()) for s, r, h in zip(slots, requests, heads)])
+  for step in range(30):
+    entries = [StepEntry(s, [r[h + step]], (0,)) for s, r, h in zip(slots, requests, heads)]
+    logits = engine.step_raw(entries, from_graph=True).float().cpu().numpy()
+    for i, h in enumerate(heads):
+      gx.check_close(logits[i:i + 1], want[i][h + step:h + step + 1], "bfloat16", f"request {i}, replayed step {step}")
+  assert engine._decode_runner.bursts >= 30
+  engine.ops.check_errors()
+
+
 # ---- configuration and model folders --------------------------------------------------------------
 
 def test_a_model_folder_gives_the_ranks_that_no_key_names(tmp_path):
