@@ -93,6 +93,30 @@ def test_long_decoding_past_windows_blocks_and_pages(where):
   engine.ops.check_errors()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_more_blocks_than_a_tile_holds_and_pages_of_64(dtype):
+  """330 tokens with blocks of 4: more block entries than one tile of 64 keys, windows that pass many
+  pages of 64, head sizes 32 and 64, four heads per kv head, a reader with a wider window."""
+  cfg_dict = gx.config(
+      [gx.attention(heads=8, kv_heads=2, dim=32, vdim=32, window=50, dims=16, base=5000.0, factor=4.0, scale=0.2),
+       gx.parallel(heads=8, kv_heads=2, dim=32, vdim=32, window=40, pool=4, scale=0.2, r_heads=4, r_kv_heads=2,
+                   r_dim=32, r_vdim=64, conv=3, ranks=(16, 8)),
+       gx.attention(heads=8, kv_heads=2, dim=32, vdim=32, window=80, dims=16, base=5000.0, factor=4.0, scale=0.2,
+                    kv_from=0),
+       gx.parallel(heads=4, kv_heads=4, dim=64, vdim=64, window=33, pool=12, scale=0.15, r_heads=2, r_kv_heads=2,
+                   r_dim=128, r_vdim=128, conv=4, ranks=(8, 8))],
+      width=128, vocab=300, ff=256)
+  cfg, t = gx.weights(cfg_dict, seed=3, matrix_std=0.1)
+  engine = gx.build_engine(cfg, t, dtype, "cuda", None, page_size=64, slots=2, max_seq_len=512)
+  toks = tokens_for(cfg_dict, 330, 1)
+  want = plain.forward(cfg_dict, gx.as_numpy(t), toks)
+  for what, cuts in [("whole", [330]), ("portions", gx.cuts_of(330, [100, 2, 37, 64, 3, 129])),
+                     ("decoding", [270] + [1] * 60)]:
+    gx.check_close(gx.run_cuts(engine, toks, cuts), want, dtype, what)
+  engine.ops.check_errors()
+
+
 # ---- a key that stands out ----------------------------------------------------------------------
 
 def needle_case(kind):
