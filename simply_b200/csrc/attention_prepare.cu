@@ -298,16 +298,37 @@ rotate_heads_kernel(const T* __restrict__ x, const int* __restrict__ positions, 
                     float sign, int H, int n, T* __restrict__ out) {
   pdl_wait_block();
   pdl_launch_dependents();
+  extern __shared__ float cs[];  // [n / 2] cos, [n / 2] sin: a token's angles are the same for all its heads
   const int t = blockIdx.x, half = n / 2;
   const float pos = sign * (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * freq[i], cs + half + i, cs + i);
+  __syncthreads();
+  constexpr int N = Vec<T>::N;
+  if (half % N == 0) {
+    for (int i0 = threadIdx.x * N; i0 < H * half; i0 += blockDim.x * N) {
+      const int h = i0 / half, pair = i0 - h * half;
+      const size_t at = ((size_t)t * H + h) * n + pair;
+      float a[N], b[N], lo[N], hi[N];
+      Vec<T>::load(x + at, a);
+      Vec<T>::load(x + at + half, b);
+#pragma unroll
+      for (int e = 0; e < N; ++e) {
+        const float c = cs[pair + e], s = cs[half + pair + e];
+        lo[e] = a[e] * c - b[e] * s;
+        hi[e] = b[e] * c + a[e] * s;
+      }
+      Vec<T>::store(out + at, lo);
+      Vec<T>::store(out + at + half, hi);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
     const int h = i / half, pair = i % half;
     const size_t at = ((size_t)t * H + h) * n + pair;
-    float sn, cs;
-    sincosf(pos * freq[pair], &sn, &cs);
+    const float c = cs[pair], s = cs[half + pair];
     const float a = to_f32<T>(x[at]), b = to_f32<T>(x[at + half]);
-    out[at] = from_f32<T>(a * cs - b * sn);
-    out[at + half] = from_f32<T>(b * cs + a * sn);
+    out[at] = from_f32<T>(a * c - b * s);
+    out[at + half] = from_f32<T>(b * c + a * s);
   }
 }
 
@@ -316,10 +337,10 @@ extern "C" int sb_rotate_heads(const void* x, int dtype, const int* positions, c
   if (num_tokens == 0) return 0;
   if (n % 2) return -4;
   if (dtype == SB_DTYPE_F32)
-    sb_launch(rotate_heads_kernel<float>, num_tokens, 256, 0, stream, (const float*)x, positions, freq, sign, H, n,
+    sb_launch(rotate_heads_kernel<float>, num_tokens, 256, (size_t)n * sizeof(float), stream, (const float*)x, positions, freq, sign, H, n,
               (float*)out);
   else
-    sb_launch(rotate_heads_kernel<bf16>, num_tokens, 256, 0, stream, (const bf16*)x, positions, freq, sign, H, n,
+    sb_launch(rotate_heads_kernel<bf16>, num_tokens, 256, (size_t)n * sizeof(float), stream, (const bf16*)x, positions, freq, sign, H, n,
               (bf16*)out);
   SB_LAUNCH_CHECK();
   return 0;

@@ -32,8 +32,9 @@ __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : l
 //   low  [T, low_width]: a (H * d) | ...
 //   conv_state [slots, taps - 1, C] float32, C = 2 G d + H dv
 // ---------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(256)
+// TAPS > 0: the number of taps at compile time, so that a channel's loads go out together.
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(512)
 delta_inputs_kernel(const T* __restrict__ pre, int pre_width, const T* __restrict__ low, int low_width,
                     const float* __restrict__ conv_w, const float* __restrict__ conv_state,
                     const float* __restrict__ dt_bias, const float* __restrict__ neg_rate,
@@ -57,11 +58,24 @@ delta_inputs_kernel(const T* __restrict__ pre, int pre_width, const T* __restric
   const float* state = conv_state + (size_t)slot * (taps - 1) * C;
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int idx = i - (taps - 1) + j;
-      const float x = idx >= 0 ? to_f32<T>(pre[(size_t)(first + idx) * pre_width + c])
-                               : state[(size_t)(taps - 1 + idx) * C + c];
-      acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+    if (TAPS > 0) {
+      float x[TAPS > 0 ? TAPS : 1], w[TAPS > 0 ? TAPS : 1];
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) {
+        const int idx = i - (TAPS - 1) + j;
+        x[j] = idx >= 0 ? to_f32<T>(pre[(size_t)(first + idx) * pre_width + c])
+                        : state[(size_t)(TAPS - 1 + idx) * C + c];
+        w[j] = conv_w[(size_t)c * TAPS + j];
+      }
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) acc = fmaf(w[j], x[j], acc);
+    } else {
+      for (int j = 0; j < taps; ++j) {
+        const int idx = i - (taps - 1) + j;
+        const float x = idx >= 0 ? to_f32<T>(pre[(size_t)(first + idx) * pre_width + c])
+                                 : state[(size_t)(taps - 1 + idx) * C + c];
+        acc = fmaf(conv_w[(size_t)c * taps + j], x, acc);
+      }
     }
     y[c] = acc * sigmoid_f32(acc);
   }
@@ -123,17 +137,26 @@ extern "C" int sb_delta_inputs(const void* pre, int pre_width, const void* low, 
   const int C = 2 * G * d + H * dv;
   const size_t smem = (size_t)C * sizeof(float);
   if (taps < 1 || G <= 0 || H % G || smem > 200 * 1024) return -13;
-  if (dtype == SB_DTYPE_F32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_inputs_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(delta_inputs_kernel<float>, num_tokens, 256, smem, stream, (const float*)pre, pre_width,
-              (const float*)low, low_width, conv_w, (const float*)conv_state, dt_bias, neg_rate, token_seq, cu_q,
-              slots, num_slots, taps, G, H, d, dv, q_out, k_out, v_out, decay_out, beta_out, err);
-  } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_inputs_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(delta_inputs_kernel<bf16>, num_tokens, 256, smem, stream, (const bf16*)pre, pre_width,
-              (const bf16*)low, low_width, conv_w, (const float*)conv_state, dt_bias, neg_rate, token_seq, cu_q,
-              slots, num_slots, taps, G, H, d, dv, q_out, k_out, v_out, decay_out, beta_out, err);
-  }
+#define SB_DELTA_INPUTS(T_, TAPS_)                                                                             \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      cudaFuncSetAttribute(delta_inputs_kernel<T_, TAPS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                           (int)smem);                                                                         \
+    sb_launch(delta_inputs_kernel<T_, TAPS_>, num_tokens, 512, smem, stream, (const T_*)pre, pre_width,        \
+              (const T_*)low, low_width, conv_w, (const float*)conv_state, dt_bias, neg_rate, token_seq, cu_q, \
+              slots, num_slots, taps, G, H, d, dv, q_out, k_out, v_out, decay_out, beta_out, err);             \
+  } while (0)
+#define SB_DELTA_INPUTS_T(T_)                    \
+  do {                                           \
+    if (taps == 4) SB_DELTA_INPUTS(T_, 4);       \
+    else if (taps == 3) SB_DELTA_INPUTS(T_, 3);  \
+    else if (taps == 2) SB_DELTA_INPUTS(T_, 2);  \
+    else SB_DELTA_INPUTS(T_, 0);                 \
+  } while (0)
+  if (dtype == SB_DTYPE_F32) SB_DELTA_INPUTS_T(float);
+  else SB_DELTA_INPUTS_T(bf16);
+#undef SB_DELTA_INPUTS_T
+#undef SB_DELTA_INPUTS
   SB_LAUNCH_CHECK();
   if (taps > 1) {
     const dim3 grid((C + 127) / 128, num_seqs);
