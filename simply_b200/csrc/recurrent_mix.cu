@@ -293,37 +293,44 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
       const float bb = buf[3 * SCAN_CHUNK * d + SCAN_CHUNK * cols_pad + i];
       float dot = 0.f, od = 0.f;
       if constexpr (VEC) {
+        // One pass over the decayed state gives both sums: with S' = diag(g) S, the result after the
+        // write is S'^T q + u (k . q), so it needs no second pass after u is known.
         float4 k4[ROWS / 4];
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f, kq = 0.f;
 #pragma unroll
         for (int r = 0; r < ROWS / 4; ++r) {
           const int at = rs + RS * r;
           if (4 * at < d) {
             const float4 g4 = reinterpret_cast<const float4*>(gg)[at];
+            const float4 q4 = reinterpret_cast<const float4*>(qq)[at];
             k4[r] = reinterpret_cast<const float4*>(kk)[at];
-            s[4 * r] *= g4.x; d0 = fmaf(s[4 * r], k4[r].x, d0);
-            s[4 * r + 1] *= g4.y; d1 = fmaf(s[4 * r + 1], k4[r].y, d1);
-            s[4 * r + 2] *= g4.z; d2 = fmaf(s[4 * r + 2], k4[r].z, d2);
-            s[4 * r + 3] *= g4.w; d3 = fmaf(s[4 * r + 3], k4[r].w, d3);
+            s[4 * r] *= g4.x; d0 = fmaf(s[4 * r], k4[r].x, d0); o0 = fmaf(s[4 * r], q4.x, o0);
+            s[4 * r + 1] *= g4.y; d1 = fmaf(s[4 * r + 1], k4[r].y, d1); o1 = fmaf(s[4 * r + 1], q4.y, o1);
+            s[4 * r + 2] *= g4.z; d2 = fmaf(s[4 * r + 2], k4[r].z, d2); o2 = fmaf(s[4 * r + 2], q4.z, o2);
+            s[4 * r + 3] *= g4.w; d3 = fmaf(s[4 * r + 3], k4[r].w, d3); o3 = fmaf(s[4 * r + 3], q4.w, o3);
+            kq = fmaf(k4[r].x, q4.x, fmaf(k4[r].y, q4.y, fmaf(k4[r].z, q4.z, fmaf(k4[r].w, q4.w, kq))));
           }
         }
         dot = (d0 + d1) + (d2 + d3);
+        od = (o0 + o1) + (o2 + o3);
 #pragma unroll
-        for (int o = 1; o < RS; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        for (int o = 1; o < RS; o <<= 1) {
+          dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          od += __shfl_xor_sync(0xffffffffu, od, o);
+          kq += __shfl_xor_sync(0xffffffffu, kq, o);
+        }
         const float u = bb * (vv - dot);
-        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
         for (int r = 0; r < ROWS / 4; ++r) {
           const int at = rs + RS * r;
           if (4 * at < d) {
-            const float4 q4 = reinterpret_cast<const float4*>(qq)[at];
-            s[4 * r] = fmaf(k4[r].x, u, s[4 * r]); o0 = fmaf(s[4 * r], q4.x, o0);
-            s[4 * r + 1] = fmaf(k4[r].y, u, s[4 * r + 1]); o1 = fmaf(s[4 * r + 1], q4.y, o1);
-            s[4 * r + 2] = fmaf(k4[r].z, u, s[4 * r + 2]); o2 = fmaf(s[4 * r + 2], q4.z, o2);
-            s[4 * r + 3] = fmaf(k4[r].w, u, s[4 * r + 3]); o3 = fmaf(s[4 * r + 3], q4.w, o3);
+            s[4 * r] = fmaf(k4[r].x, u, s[4 * r]);
+            s[4 * r + 1] = fmaf(k4[r].y, u, s[4 * r + 1]);
+            s[4 * r + 2] = fmaf(k4[r].z, u, s[4 * r + 2]);
+            s[4 * r + 3] = fmaf(k4[r].w, u, s[4 * r + 3]);
           }
         }
-        od = (o0 + o1) + (o2 + o3);
+        od = fmaf(u, kq, od);
       } else {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
@@ -344,9 +351,9 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
             od = fmaf(s[r], qq[row], od);
           }
         }
-      }
 #pragma unroll
-      for (int o = 1; o < RS; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
+        for (int o = 1; o < RS; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
+      }
       if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = od;
     }
     __syncthreads();  // the buffer is filled again two chunks on
