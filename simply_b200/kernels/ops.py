@@ -792,11 +792,11 @@ class CudaOps:
       pool_args = (_ptr(pool), _ptr(pool_table), pool_table.shape[1] if pool is not None else 0, int(pool_len),
                    pool.shape[0] if pool is not None else 0)
 
-      def general(token_list, count):
+      def general():
         self._call("sb_paged_attention_general", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
-                   block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), count, num_heads,
+                   block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
                    num_kv_heads, head_dim, value_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
-                   int(window or 0), *pool_args, _ptr(token_list), _ptr(self.err))
+                   int(window or 0), *pool_args, None, _ptr(self.err))
 
       # bfloat16 with key size = value size: the tensor-core tile kernel (mma.sync tiles of 64 rows,
       # the block entries in tiles of their own ahead of the tokens) for prompt portions and single
@@ -804,7 +804,7 @@ class CudaOps:
       tensor_cores = (pooled is not None and value_dim == head_dim and q.dtype == torch.bfloat16 and window
                       and self._uses_tensor_core_attention(head_dim, group))
       if not tensor_cores:
-        general(None, t)
+        general()
         return out
       key = self._plan_key(window, group, num_kv_heads, head_dim, ctx.page_size) + ("pooled", pool_len)
       plan = ctx.memo.get(key)  # (a decode graph brings its static list)
