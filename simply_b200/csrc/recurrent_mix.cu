@@ -184,7 +184,7 @@ extern "C" int sb_delta_inputs(const void* pre, int pre_width, const void* low, 
 // g, v and beta of SCAN_CHUNK tokens at a time come to shared memory by cp.async, the next
 // chunk while the block works on this one.
 // ---------------------------------------------------------------------------
-#define SCAN_CHUNK 16
+#define SCAN_CHUNK chunk  // tokens per fetch: a kernel argument (the buffers' layout depends on it)
 #define SCAN_ROWS 32
 
 __device__ __forceinline__ void scan_copy4(float* smem, const float* gmem) {
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                   const float* __restrict__ decay, const float* __restrict__ beta, float* __restrict__ state,
                   const int* __restrict__ cu_q, const int* __restrict__ slots, int num_slots, int G, int H, int d,
-                  int dv, int cols, float* __restrict__ out, int* err) {
+                  int dv, int cols, int chunk, float* __restrict__ out, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
   // Two buffers of: k [CHUNK][d], q [CHUNK][d], g [CHUNK][d], v [CHUNK][cols], beta [CHUNK].
@@ -369,7 +369,7 @@ delta_scan_kernel(const float* __restrict__ q, const float* __restrict__ k, cons
 
 extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, const float* decay, const float* beta,
                              float* state, const int* cu_q, const int* slots, int num_seqs, int num_slots, int G,
-                             int H, int d, int dv, float* out, int* err, cudaStream_t stream) {
+                             int H, int d, int dv, int max_q_len, float* out, int* err, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (d <= 0 || d > 32 * SCAN_ROWS || dv <= 0 || G <= 0 || H % G) return -13;
   // Rows per thread: 8 where the head allows (a column over at most 32 lanes), else 32.
@@ -377,12 +377,19 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
   const int rows = (vec && d <= 8 * 32) ? 8 : SCAN_ROWS;
   int rs = 1;
   while (rs * rows < d) rs <<= 1;
-  const int threads = 128;
+  // Long walks: blocks of 128 threads even when that leaves SMs without one (every block fetches its
+  // head's k, q and g, so narrower blocks fetch them more often) and chunks of 16 tokens (a
+  // 2,048-token prompt of 16 heads: 0.84 ms; 0.90 with chunks of 8; 1.02 with 64 threads).  Steps of
+  // a few tokens read and write the state and little else: narrow blocks with small buffers, many
+  // to an SM.
+  const bool long_walk = max_q_len >= 64;
+  const int threads = long_walk ? 128 : 64;
+  int chunk = 1;
+  while (chunk < 16 && chunk < max_q_len) chunk <<= 1;
+  if (long_walk && (size_t)2 * 16 * (3 * d + 36) * sizeof(float) > 200 * 1024) chunk = 8;
   int cols = threads / rs;
+  if (cols < 1) cols = 1;
   if (cols > dv) cols = dv;
-  // (Blocks of 128 threads even when that leaves SMs without one: every block fetches its head's k,
-  // q and g, so narrower blocks fetch them more often.  A 2,048-token prompt of 16 heads: 0.90 ms
-  // with 128 threads, 1.02 with 64; chunks of 16 tokens instead of 8 give another 6 %.)
   const int block = ((cols * rs + 31) / 32) * 32;
   const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
   const size_t smem = (size_t)2 * SCAN_CHUNK * (3 * d + ((cols + 3) & ~3) + 4) * sizeof(float);
@@ -393,7 +400,7 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
       cudaFuncSetAttribute(delta_scan_kernel<RS_, ROWS_, VEC_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                                        \
     sb_launch(delta_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, q, k, v, decay, beta, state,   \
-              cu_q, slots, num_slots, G, H, d, dv, cols, out, err);                                           \
+              cu_q, slots, num_slots, G, H, d, dv, cols, chunk, out, err);                                           \
   } while (0)
 #define SB_SCAN(RS_)                                  \
   do {                                                \

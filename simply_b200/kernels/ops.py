@@ -253,7 +253,7 @@ class CudaOps:
                             c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void, c_void,
                             c_void, c_void, c_void, c_void],
         "sb_delta_scan": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int,
-                          c_int, c_int, c_int, c_void, c_void, c_void],
+                          c_int, c_int, c_int, c_int, c_void, c_void, c_void],
         "sb_gated_head_norm": [c_void, c_void, c_int, c_int, c_int, c_void, c_float, c_int, c_int, c_int, c_void,
                                c_void],
         "sb_normed_mean": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_float,
@@ -929,7 +929,7 @@ class CudaOps:
     out = self._new(q.shape[0], num_heads, value_dim, dtype=torch.float32)
     self._call("sb_delta_scan", _ptr(q), _ptr(k), _ptr(v), _ptr(decay), _ptr(beta), _ptr(state), _ptr(ctx.cu_q),
                _ptr(ctx.slots), ctx.num_seqs, state.shape[0], num_kv_heads, num_heads, head_dim, value_dim,
-               _ptr(out), _ptr(self.err))
+               ctx.max_q_len, _ptr(out), _ptr(self.err))
     return out
 
   def gated_head_norm(self, o: torch.Tensor, low: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float,
