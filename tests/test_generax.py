@@ -324,3 +324,83 @@ def test_configurations_that_cannot_run_are_refused():
   for change in cases:
     with pytest.raises(ConfigError):
       config_from_dict(broken(change))
+
+
+# ---- the command line -----------------------------------------------------------------------------
+
+def _cli(*args):
+  import subprocess
+  import sys
+  repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  env = dict(os.environ, PYTHONPATH=repo + os.pathsep + os.environ.get("PYTHONPATH", ""))
+  p = subprocess.run([sys.executable, "-m", "simply_b200", *args], capture_output=True, text=True, env=env, cwd=repo,
+                     timeout=900)
+  assert p.returncode == 0, p.stderr[-2000:]
+  return [json.loads(line) for line in p.stdout.splitlines() if line.startswith("{")]
+
+
+def test_the_command_line_writes_a_generax_folder(tmp_path):
+  out = str(tmp_path / "m")
+  assert _cli("--experiment_config", "generax-tiny", "--write_model_dir", out, "--model_seed", "1",
+              "--matrix_std", "0.2", "--scale_std", "0.1") == [{"wrote": out}]
+  with open(os.path.join(out, "config.json")) as f:
+    d = json.load(f)
+  assert d["architecture"] == "Generax" and [l["type"] for l in d["layers"]] == ["parallel", "attention", "attention"]
+  cfg = load_config(out)
+  assert cfg.to_dict() == d
+  engine = Engine.from_folder(out, EngineConfig(activation_dtype="float32", page_size=8, batch_size=2, max_seq_len=64),
+                              ops=ReferenceOps(torch.float32))
+  r = engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_decode_steps=4))
+  assert len(r[0].output_token_ids) == 4
+
+
+@pytest.mark.gpu
+def test_the_command_line_generates_from_a_generax_folder(tmp_path):
+  out = str(tmp_path / "m")
+  _cli("--experiment_config", "generax-tiny", "--write_model_dir", out, "--model_seed", "1", "--matrix_std", "0.2",
+       "--scale_std", "0.1")
+  lines = _cli("--ckpt_dir", out, "--prompt_ids", "1,2,3;9,8,7,6,5", "--temperature", "0", "--max_decode_steps", "12",
+               "--activation_dtype", "float32", "--max_seq_len", "128", "--batch_size", "2")
+  assert [len(l["output_token_ids"]) for l in lines] == [12, 12]
+  from simply_b200.weights import safetensors_io as st
+  reader = st.TensorReader(st.index_files(st.model_files(out)))
+  w = {k: reader.read(k).float().numpy() for k in reader.entries}
+  with open(os.path.join(out, "config.json")) as f:
+    d = json.load(f)
+  for line in lines:
+    toks = list(line["input_token_ids"])
+    for _ in range(12):
+      toks.append(int(np.argmax(plain.forward(d, w, toks)[-1])))
+    assert line["output_token_ids"] == toks[len(line["input_token_ids"]):]
+  lines = _cli("--experiment_config", "generax-tiny", "--random_weights", "--prompt_ids", "4,5,6", "--max_decode_steps", "5",
+               "--max_seq_len", "128")
+  assert len(lines[0]["output_token_ids"]) == 5
+
+
+# ---- the replay tool, as a user runs it ---------------------------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_replay_tool_four_ways(tmp_path, dtype):
+  """bin/trace_run as a child process on a folder of this design: every request whole, prompt then
+  single tokens, changing portions, and several live requests in a pool that holds only what is
+  live at once (pages and slots come back), against the plain model."""
+  from tests import trace_util
+  cfg = config_from_dict(dict(gx.CONFIG_B, max_context=1024))
+  folder = write_model_folder(cfg, 4, str(tmp_path / "m"), matrix_std=0.2, scale_std=0.15)
+  from simply_b200.weights import safetensors_io as st
+  reader = st.TensorReader(st.index_files(st.model_files(folder)))
+  w = {k: reader.read(k).float().numpy() for k in reader.entries}
+  with open(os.path.join(folder, "config.json")) as f:
+    d = json.load(f)
+  rng = np.random.default_rng(8)
+  requests = {f"q{i}": rng.integers(0, d["vocab"], n).tolist() for i, n in enumerate((150, 70, 1, 97, 40, 131))}
+  want = {rid: plain.forward(d, w, toks) for rid, toks in requests.items()}
+  ways = {"whole": trace_util.whole(requests), "decode": trace_util.prefill_then_decode(requests, tail=40),
+          "portions": trace_util.changing_portions(requests), "mixed": trace_util.mixed(requests, seed=1)}
+  for name, steps in ways.items():
+    out = str(tmp_path / f"{name}_{dtype}")
+    trace_util.run_tool(folder, dtype, steps, out, trace_util.tokens_needed(steps), extra=("--poison-freed-pages",))
+    got = trace_util.collect(steps, out, d["vocab"])
+    for rid, rows in got.items():
+      gx.check_close(np.stack([rows[p] for p in sorted(rows)]), want[rid], dtype, f"{name}: {rid}")
