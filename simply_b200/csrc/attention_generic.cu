@@ -16,8 +16,7 @@
 // window W and blocks of P tokens, position i also sees, ahead of its window and under the same
 // softmax, one key and value per block c with c*P + P - 1 <= i - W, read from a second paged
 // storage that holds one entry per P tokens in the page of the block's first token.  Blocks
-// are visited in tiles of 32 by block number, before the tokens.  `token_list` restricts the
-// launch to some of the step's tokens.
+// are visited in tiles of 32 by block number, before the tokens.
 //
 // This is the true 32-bit path's attention and the fallback of the bfloat16
 // path for shapes its tensor-core kernels refuse.
@@ -117,16 +116,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ ca
                                T* __restrict__ out, int num_tokens, int num_q_heads, int num_kv_heads,
                                int head_dim, int v_dim, int page_size, int num_pages, float cap, int window,
                                const T* __restrict__ pool, const int* __restrict__ pool_table,
-                               int pool_max_pages, int pool_len, int pool_pages,
-                               const int* __restrict__ token_list, int* err) {
+                               int pool_max_pages, int pool_len, int pool_pages, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
   // head_dim floats of q, then per warp its running maximum, sum and v_dim partial results
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long item = blockIdx.x;
-  const int listed = (int)(item / num_q_heads), n = (int)(item % num_q_heads);
-  const int t = token_list != nullptr ? token_list[listed] : listed;
+  const int t = (int)(item / num_q_heads), n = (int)(item % num_q_heads);
   const int m = n / (num_q_heads / num_kv_heads);
   const int b = token_seq[t], pos = positions[t];
   float* qs = smem;
@@ -221,8 +218,8 @@ extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* 
                                           void* out, int num_tokens, int num_q_heads, int num_kv_heads,
                                           int head_dim, int v_dim, int page_size, int num_pages, float cap,
                                           int window, const void* pool, const int* pool_table,
-                                          int pool_max_pages, int pool_len, int pool_pages,
-                                          const int* token_list, int* err, cudaStream_t stream) {
+                                          int pool_max_pages, int pool_len, int pool_pages, int* err,
+                                          cudaStream_t stream) {
   if (num_tokens == 0) return 0;
   if (head_dim <= 0 || head_dim > 32 * GEN_MAX_DPL || v_dim <= 0 || v_dim > 32 * GEN_MAX_DPL) return -7;
   if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return -8;
@@ -234,12 +231,12 @@ extern "C" int sb_paged_attention_general(const void* q, int dtype, const void* 
     sb_launch(paged_attention_generic_kernel<float>, blocks, GEN_WARPS * 32, smem, stream, (const float*)q,
         (const float*)cache, block_table, max_pages, token_seq, positions, (float*)out, num_tokens,
         num_q_heads, num_kv_heads, head_dim, v_dim, page_size, num_pages, cap, window, (const float*)pool, pool_table,
-        pool_max_pages, pool_len, pool_pages, token_list, err);
+        pool_max_pages, pool_len, pool_pages, err);
   else
     sb_launch(paged_attention_generic_kernel<bf16>, blocks, GEN_WARPS * 32, smem, stream, (const bf16*)q,
         (const bf16*)cache, block_table, max_pages, token_seq, positions, (bf16*)out, num_tokens,
         num_q_heads, num_kv_heads, head_dim, v_dim, page_size, num_pages, cap, window, (const bf16*)pool, pool_table,
-        pool_max_pages, pool_len, pool_pages, token_list, err);
+        pool_max_pages, pool_len, pool_pages, err);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -251,5 +248,5 @@ extern "C" int sb_paged_attention_generic(const void* q, int dtype, const void* 
                                           int* err, cudaStream_t stream) {
   return sb_paged_attention_general(q, dtype, cache, block_table, max_pages, token_seq, positions, out, num_tokens,
                                     num_q_heads, num_kv_heads, head_dim, head_dim, page_size, num_pages, cap,
-                                    window, nullptr, nullptr, 0, 0, 0, nullptr, err, stream);
+                                    window, nullptr, nullptr, 0, 0, 0, err, stream);
 }

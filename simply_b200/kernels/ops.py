@@ -242,7 +242,7 @@ class CudaOps:
                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void],
         "sb_paged_attention_general": [c_void, c_int, c_void, c_void, c_int, c_void, c_void, c_void, c_int,
                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void, c_void,
-                                       c_int, c_int, c_int, c_void, c_void, c_void],
+                                       c_int, c_int, c_int, c_void, c_void],
         "sb_qk_norm_rotate_store": [c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_int, c_void,
                                     c_void, c_void, c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_void, c_void],
@@ -796,7 +796,7 @@ class CudaOps:
         self._call("sb_paged_attention_general", _ptr(q), _code(q), _ptr(storage), _ptr(block_table),
                    block_table.shape[1], _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(out), t, num_heads,
                    num_kv_heads, head_dim, value_dim, ctx.page_size, storage.shape[0], float(logit_softcap),
-                   int(window or 0), *pool_args, None, _ptr(self.err))
+                   int(window or 0), *pool_args, _ptr(self.err))
 
       # bfloat16 with key size = value size: the tensor-core tile kernel (mma.sync tiles of 64 rows,
       # the block entries in tiles of their own ahead of the tokens) for prompt portions and single
