@@ -59,12 +59,14 @@ extern "C" int sb_embed(const void* table, int table_dtype, const int* ids, floa
 //   b   = branch row                      (optional)
 //   b   = b * rsqrt(mean(b^2) + eps_post) * (w_post [+ 1])   (if w_post)
 //   h  += b                               (written back unless rows are gathered)
+//   h  += branch2 row                     (optional, only beside a branch: a block whose two
+//                                          sublayers read one norm adds both results)
 //   y   = h * rsqrt(mean(h^2) + eps_pre) * (w_pre [+ 1])     (if w_pre), stored as T
 // With `rows`, block r works on row rows[r] and writes y[r]; h is left untouched.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict__ branch,
-                                     const void* __restrict__ w_post, int post_f32, float eps_post,
+                                     const T* __restrict__ branch2, const void* __restrict__ w_post, int post_f32, float eps_post,
                                      int post_plus_one, const void* __restrict__ w_pre, int pre_f32,
                                      float eps_pre, int pre_plus_one, const int* __restrict__ rows,
                                      T* __restrict__ y, int width, int num_rows_total, int* err) {
@@ -97,11 +99,12 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
     // the kernel pays one memory latency instead of one per pass.  Same arithmetic as below.
     const int i = threadIdx.x * N;
     const bool on = i < width;
-    float b[N], v[N];
+    float b[N], b2[N], v[N];
 #pragma unroll
-    for (int k = 0; k < N; ++k) b[k] = v[k] = 0.f;
+    for (int k = 0; k < N; ++k) b[k] = b2[k] = v[k] = 0.f;
     if (on) {
       if (branch) Vec<T>::load(branch + (size_t)src * width + i, b);
+      if (branch2) Vec<T>::load(branch2 + (size_t)src * width + i, b2);
 #pragma unroll
       for (int k = 0; k < N; k += 4) Vec<float>::load(hp + i + k, v + k);
     }
@@ -119,6 +122,7 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
         float bb = b[k];
         if (w_post) bb = bb * rstd_b * (wp[k] + post_one);
         v[k] += bb;
+        v[k] += b2[k];
       }
       if (!rows && on) {
 #pragma unroll
@@ -180,6 +184,12 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
           if (w_post) b = b * rstd_b * (w[k] + post_one);
           v[k] += b;
         }
+        if (branch2) {
+          float c[N];
+          Vec<T>::load(branch2 + (size_t)src * width + i, c);
+#pragma unroll
+          for (int k = 0; k < N; ++k) v[k] += c[k];
+        }
         if (!rows) {
 #pragma unroll
           for (int k = 0; k < N; k += 4) Vec<float>::store(hp + i + k, v + k);
@@ -198,6 +208,7 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
         float b = row[i];
         if (w_post) b = b * rstd_b * (load_scalar(w_post, post_f32, i) + post_one);
         v += b;
+        if (branch2) v += to_f32<T>(branch2[(size_t)src * width + i]);
         if (!rows) hp[i] = v;
       }
       row[i] = v;
@@ -223,7 +234,8 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
   }
 }
 
-extern "C" int sb_residual_norm(float* h, const void* branch, int dtype, const void* w_post, int post_f32,
+extern "C" int sb_residual_norm(float* h, const void* branch, const void* branch2, int dtype, const void* w_post,
+                                int post_f32,
                                 float eps_post, int post_plus_one, const void* w_pre, int pre_f32,
                                 float eps_pre, int pre_plus_one, const int* rows, void* y, int num_rows,
                                 int width, int num_rows_total, int* err, cudaStream_t stream) {
@@ -241,12 +253,12 @@ extern "C" int sb_residual_norm(float* h, const void* branch, int dtype, const v
   if (dtype == SB_DTYPE_F32) {
     auto k = residual_norm_kernel<float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(k, num_rows, threads, smem, stream, h, (const float*)branch, w_post, post_f32, eps_post,
+    sb_launch(k, num_rows, threads, smem, stream, h, (const float*)branch, (const float*)branch2, w_post, post_f32, eps_post,
         post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (float*)y, width, num_rows_total, err);
   } else {
     auto k = residual_norm_kernel<bf16>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(k, num_rows, threads, smem, stream, h, (const bf16*)branch, w_post, post_f32, eps_post,
+    sb_launch(k, num_rows, threads, smem, stream, h, (const bf16*)branch, (const bf16*)branch2, w_post, post_f32, eps_post,
         post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (bf16*)y, width, num_rows_total, err);
   }
   SB_LAUNCH_CHECK();

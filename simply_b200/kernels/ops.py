@@ -218,7 +218,7 @@ class CudaOps:
     c_int, c_float, c_void, c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
     protos = {
         "sb_embed": [c_void, c_int, c_void, c_float, c_void, c_int, c_int, c_int, c_void, c_void],
-        "sb_residual_norm": [c_void, c_void, c_int, c_void, c_int, c_float, c_int, c_void, c_int, c_float,
+        "sb_residual_norm": [c_void, c_void, c_void, c_int, c_void, c_int, c_float, c_int, c_void, c_int, c_float,
                              c_int, c_void, c_void, c_int, c_int, c_int, c_void, c_void],
         "sb_rms_norm": [c_void, c_int, c_void, c_int, c_float, c_int, c_void, c_int, c_int, c_int, c_void],
         "sb_gather_rows": [c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_void, c_void],
@@ -682,8 +682,9 @@ class CudaOps:
     return out
 
   def residual_norm(self, h: torch.Tensor, branch: torch.Tensor | None, post: Any, pre: Any,
-                    rows: torch.Tensor | None) -> torch.Tensor | None:
-    """h += norm_post(branch); returns norm_pre(h) in the activation dtype (see csrc/elementwise.cu)."""
+                    rows: torch.Tensor | None, branch2: torch.Tensor | None = None) -> torch.Tensor | None:
+    """h += norm_post(branch) (+ branch2, as it is); returns norm_pre(h) in the activation dtype (see
+    csrc/elementwise.cu)."""
     width = h.shape[1]
     num_rows = h.shape[0] if rows is None else rows.numel()
     y = self._new(num_rows, width) if pre is not None else None
@@ -691,9 +692,13 @@ class CudaOps:
       return None
     if branch is not None and branch.dtype != self.dtype:
       branch = self.cast(branch, self.dtype)
+    if branch2 is not None and branch2.dtype != self.dtype:
+      branch2 = self.cast(branch2, self.dtype)
+    if branch2 is not None and branch is None:
+      branch, branch2 = branch2, None
     wp, wq = (post.weight if post is not None else None), (pre.weight if pre is not None else None)
     self._call(
-        "sb_residual_norm", _ptr(h), _ptr(branch), _BF16 if self.dtype == torch.bfloat16 else _F32,
+        "sb_residual_norm", _ptr(h), _ptr(branch), _ptr(branch2), _BF16 if self.dtype == torch.bfloat16 else _F32,
         _ptr(wp), int(wp is not None and wp.dtype == torch.float32),
         float(post.eps) if post is not None else 0.0, int(post.plus_one) if post is not None else 0,
         _ptr(wq), int(wq is not None and wq.dtype == torch.float32),

@@ -30,14 +30,19 @@ from simply_b200.weights.loader import TensorSpec
 
 
 class ResidualStream:
-  """float32 [T, width] plus at most one branch that is still to be added."""
+  """float32 [T, width] plus what is still to be added: a branch with its post-norm, and beside it a
+  second branch that is added as it is (the two sublayers of a block whose norm they share)."""
 
   def __init__(self, h: torch.Tensor):
     self.h = h
     self._branch: torch.Tensor | None = None
     self._post: Norm | None = None
+    self._second: torch.Tensor | None = None
 
   def add(self, branch: torch.Tensor, post_norm: Norm | None, ctx: Any) -> None:
+    if self._branch is not None and self._second is None and post_norm is None:
+      self._second = branch  # rides along: h + first + second in one kernel
+      return
     self.flush(ctx)
     self._branch, self._post = branch, post_norm
 
@@ -52,22 +57,27 @@ class ResidualStream:
 
   def _combine(self, pre: Norm | None, ctx: Any, rows: torch.Tensor | None):
     ops = ctx.ops
-    branch, post = self._branch, self._post
+    branch, post, second = self._branch, self._post, self._second
     fusable = (post is None or isinstance(post, RMSNorm)) and (pre is None or isinstance(pre, RMSNorm))
-    if fusable:
+    if fusable and second is None:
       out = ops.residual_norm(self.h, branch, post, pre, rows)
+    elif fusable:
+      out = ops.residual_norm(self.h, branch, post, pre, rows, branch2=second)
     else:
       # Norms the fused kernel does not know: compose from their own `apply`.
       if rows is not None:
         h = ops.gather_rows(self.h, rows)
         branch = ops.gather_rows(branch, rows) if branch is not None else None
+        second = ops.gather_rows(second, rows) if second is not None else None
       else:
         h = self.h
       if branch is not None:
         ops.add_to_residual(h, post.apply(branch, ctx) if post is not None else branch)
+      if second is not None:
+        ops.add_to_residual(h, second)
       out = pre.apply(h, ctx) if pre is not None else None
     if rows is None:
-      self._branch = self._post = None
+      self._branch = self._post = self._second = None
     return out
 
 

@@ -78,14 +78,17 @@ class ReferenceOps:
   def rms_norm(self, x, w, eps, plus_one):
     return self._rms(x, w, eps, plus_one).to(self.dtype)
 
-  def residual_norm(self, h, branch, post, pre, rows):
+  def residual_norm(self, h, branch, post, pre, rows, branch2=None):
     if rows is not None:
       idx = rows.long()
       h = h[idx].clone()
       branch = branch[idx] if branch is not None else None
+      branch2 = branch2[idx] if branch2 is not None else None
     if branch is not None:
       b = self._rms(branch, post.weight, post.eps, post.plus_one) if post is not None else branch.float()
       h += b
+    if branch2 is not None:
+      h += branch2.float()
     if pre is None:
       return None
     return self._rms(h, pre.weight, pre.eps, pre.plus_one).to(self.dtype)

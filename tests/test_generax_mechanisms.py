@@ -194,3 +194,29 @@ def test_norm_over_whole_projections_rotations_and_the_cache(sizes, where):
     close(back.float().cpu().numpy(), flat.float().cpu().numpy(), dtype, "there and back")
     want = plain.rotary(flat.float().cpu().numpy().astype(np.float64).reshape(n, heads, dv), pos, dv, base)
     close(there.float().cpu().numpy().reshape(n, heads, dv), want, dtype, "turned")
+
+
+@pytest.mark.parametrize("where", WHERE)
+@pytest.mark.parametrize("width", [48, 50, 4096])
+def test_two_branches_join_the_stream_in_one_step(width, where):
+  """h += first + second, then the next norm: what a block adds whose sublayers share one norm."""
+  from simply_b200.parts.norm import RMSNorm
+  ops, dtype = table(where)
+  device = where[1]
+  rng = np.random.default_rng(width)
+  n, eps = 7, 1e-5
+  h = rng.standard_normal((n, width)).astype(np.float32)
+  first, second = (rounded(rng.standard_normal((n, width)), dtype) for _ in range(2))
+  norm = RMSNorm("n", width, eps, plus_one=False)
+  norm.weight = torch.from_numpy((1 + 0.2 * rng.standard_normal(width)).astype(np.float32)).to(device)
+  want_h = h.astype(np.float64) + first.float().numpy() + second.float().numpy()
+  want_y = plain.rms_norm(want_h, norm.weight.float().cpu().numpy().astype(np.float64), eps)
+  stream = torch.from_numpy(h.copy()).to(device)
+  y = ops.residual_norm(stream, first.to(device), None, norm, None, branch2=second.to(device))
+  close(stream.cpu().numpy(), want_h, torch.float32, "stream")
+  close(y.float().cpu().numpy(), want_y, dtype, "normed")
+  rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=device)
+  stream = torch.from_numpy(h.copy()).to(device)
+  y = ops.residual_norm(stream, first.to(device), None, norm, rows, branch2=second.to(device))
+  close(y.float().cpu().numpy(), want_y[[5, 0, 5]], dtype, "gathered rows")
+  close(stream.cpu().numpy(), h, torch.float32, "the stream is left alone when rows are gathered")
