@@ -64,7 +64,7 @@ extern "C" int sb_embed(const void* table, int table_dtype, const int* ids, floa
 //   y   = h * rsqrt(mean(h^2) + eps_pre) * (w_pre [+ 1])     (if w_pre), stored as T
 // With `rows`, block r works on row rows[r] and writes y[r]; h is left untouched.
 // ---------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool TWO>  // TWO: with a second branch (the usual kernel is compiled without it)
 __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict__ branch,
                                      const T* __restrict__ branch2, const void* __restrict__ w_post, int post_f32, float eps_post,
                                      int post_plus_one, const void* __restrict__ w_pre, int pre_f32,
@@ -99,12 +99,16 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
     // the kernel pays one memory latency instead of one per pass.  Same arithmetic as below.
     const int i = threadIdx.x * N;
     const bool on = i < width;
-    float b[N], b2[N], v[N];
+    float b[N], b2[TWO ? N : 1], v[N];
 #pragma unroll
-    for (int k = 0; k < N; ++k) b[k] = b2[k] = v[k] = 0.f;
+    for (int k = 0; k < N; ++k) b[k] = v[k] = 0.f;
+    if constexpr (TWO) {
+#pragma unroll
+      for (int k = 0; k < N; ++k) b2[k] = 0.f;
+    }
     if (on) {
       if (branch) Vec<T>::load(branch + (size_t)src * width + i, b);
-      if (branch2) Vec<T>::load(branch2 + (size_t)src * width + i, b2);
+      if constexpr (TWO) Vec<T>::load(branch2 + (size_t)src * width + i, b2);
 #pragma unroll
       for (int k = 0; k < N; k += 4) Vec<float>::load(hp + i + k, v + k);
     }
@@ -122,7 +126,7 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
         float bb = b[k];
         if (w_post) bb = bb * rstd_b * (wp[k] + post_one);
         v[k] += bb;
-        v[k] += b2[k];
+        if constexpr (TWO) v[k] += b2[k];
       }
       if (!rows && on) {
 #pragma unroll
@@ -184,7 +188,7 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
           if (w_post) b = b * rstd_b * (w[k] + post_one);
           v[k] += b;
         }
-        if (branch2) {
+        if constexpr (TWO) {
           float c[N];
           Vec<T>::load(branch2 + (size_t)src * width + i, c);
 #pragma unroll
@@ -208,7 +212,7 @@ __global__ void residual_norm_kernel(float* __restrict__ h, const T* __restrict_
         float b = row[i];
         if (w_post) b = b * rstd_b * (load_scalar(w_post, post_f32, i) + post_one);
         v += b;
-        if (branch2) v += to_f32<T>(branch2[(size_t)src * width + i]);
+        if constexpr (TWO) v += to_f32<T>(branch2[(size_t)src * width + i]);
         if (!rows) hp[i] = v;
       }
       row[i] = v;
@@ -250,17 +254,21 @@ extern "C" int sb_residual_norm(float* h, const void* branch, const void* branch
   int threads = width >= 2048 ? 512 : 256;
   if (width % vec == 0 && width / vec <= 1024) threads = ((width / vec + 31) / 32) * 32;
   if (threads < 64) threads = 64;
+  if (branch2 != nullptr && branch == nullptr) return -3;
+#define SB_RESIDUAL(T_, TWO_)                                                                                    \
+  do {                                                                                                           \
+    auto k = residual_norm_kernel<T_, TWO_>;                                                                     \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    sb_launch(k, num_rows, threads, smem, stream, h, (const T_*)branch, (const T_*)branch2, w_post, post_f32,    \
+              eps_post, post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (T_*)y, width, num_rows_total, \
+              err);                                                                                              \
+  } while (0)
   if (dtype == SB_DTYPE_F32) {
-    auto k = residual_norm_kernel<float>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(k, num_rows, threads, smem, stream, h, (const float*)branch, (const float*)branch2, w_post, post_f32, eps_post,
-        post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (float*)y, width, num_rows_total, err);
+    if (branch2) SB_RESIDUAL(float, true); else SB_RESIDUAL(float, false);
   } else {
-    auto k = residual_norm_kernel<bf16>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(k, num_rows, threads, smem, stream, h, (const bf16*)branch, (const bf16*)branch2, w_post, post_f32, eps_post,
-        post_plus_one, w_pre, pre_f32, eps_pre, pre_plus_one, rows, (bf16*)y, width, num_rows_total, err);
+    if (branch2) SB_RESIDUAL(bf16, true); else SB_RESIDUAL(bf16, false);
   }
+#undef SB_RESIDUAL
   SB_LAUNCH_CHECK();
   return 0;
 }
