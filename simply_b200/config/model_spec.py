@@ -47,11 +47,14 @@ class LayerCall:
     (named "<layer>#<index in run order>").  Naming another call's cache makes
     this call read (and, if `writes_cache`, also extend) that cache.
   writes_cache: False for a call that only reads a cache another call wrote.
+  add_embedding: True adds the embedding's output (the stream as it stood before the first
+    layer) to the stream once more, right before this call.
   """
 
   layer: str
   cache: str | None = None
   writes_cache: bool = True
+  add_embedding: bool = False
 
 
 @dataclasses.dataclass(frozen=True)

@@ -345,3 +345,149 @@ extern "C" int sb_rotate_heads(const void* x, int dtype, const int* positions, c
   SB_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Attention whose heads are normed one by one after rotation.  One block per token, a warp per
+// head.  Row of `proj`: q (H d) | k (G d) | [v (G dv)] | whatever follows (a gate, which this
+// kernel does not read).
+//   (a, b) = (a cos - b sin, b cos + a sin)     neighbours (2i, 2i + 1) for `interleaved`, else
+//                                               (i, i + rot_dims/2); angle = pos * rot_freq[i]
+//   x      = x / sqrt(mean_head x^2 + eps)      (no scale; `head_norm` = 0 skips it)
+//   q     *= q_scale
+// Keys go to the cache rotated and normed.  Values: with `tie_values` a key head as the projection
+// left it (before rotation and norm) is also the value head; otherwise the v columns as they are.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotate_headnorm_store_kernel(const T* __restrict__ proj, int row_width, float eps, float q_scale,
+                             const float* __restrict__ rot_freq, int rot_dims, int interleaved, int head_norm,
+                             int tie_values, T* __restrict__ q_out, T* __restrict__ cache,
+                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ token_seq,
+                             const int* __restrict__ positions, int H, int G, int d, int dv, int page_size,
+                             int num_pages, int write_cache, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ float row[];  // (H + G) d floats, then cos and sin of rot_dims / 2 angles
+  const int nq = H * d, nk = G * d, half = rot_dims / 2;
+  float* cs = row + nq + nk;
+  const int t = blockIdx.x;
+  const T* x = proj + (size_t)t * row_width;
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(pos * rot_freq[i], cs + half + i, cs + i);
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) row[i] = to_f32<T>(x[i]);
+  __syncthreads();
+
+  long long page = -1;
+  int off = 0;
+  if (write_cache && nk > 0) {
+    const int p = positions[t];
+    page = block_table[(size_t)token_seq[t] * max_pages + p / page_size];
+    off = p % page_size;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_PAGE);
+      page = -1;
+    }
+  }
+  const size_t page_stride = (size_t)G * page_size * (d + dv);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int head = warp; head < H + G; head += nwarps) {
+    float* v = row + (size_t)head * d;
+    const bool is_q = head < H;
+    T* value_dst = nullptr;
+    T* key_dst = nullptr;
+    if (!is_q && page >= 0) {
+      key_dst = cache + page * page_stride + ((size_t)(head - H) * page_size + off) * d;
+      value_dst = cache + page * page_stride + (size_t)G * page_size * d + ((size_t)(head - H) * page_size + off) * dv;
+      if (tie_values)  // the head as projected, before this warp turns it
+        for (int c = lane; c < d; c += 32) value_dst[c] = from_f32<T>(v[c]);
+    }
+    __syncwarp();
+    for (int i = lane; i < half; i += 32) {
+      const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+      const float a = v[ia], b = v[ib], c = cs[i], sn = cs[half + i];
+      v[ia] = a * c - b * sn;
+      v[ib] = b * c + a * sn;
+    }
+    __syncwarp();
+    float scale = is_q ? q_scale : 1.0f;
+    if (head_norm) {
+      float ss = 0.f;
+      for (int c = lane; c < d; c += 32) ss = fmaf(v[c], v[c], ss);
+      ss = warp_sum(ss);
+      scale *= 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    if (is_q) {
+      T* dst = q_out + (size_t)t * nq + (size_t)head * d;
+      for (int c = lane; c < d; c += 32) dst[c] = from_f32<T>(v[c] * scale);
+    } else if (key_dst != nullptr) {
+      for (int c = lane; c < d; c += 32) key_dst[c] = from_f32<T>(v[c] * scale);
+    }
+  }
+  if (!tie_values && page >= 0) {
+    const T* vx = x + nq + nk;
+    T* dst = cache + page * page_stride + (size_t)G * page_size * d;
+    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+      const int m = i / dv, c = i - m * dv;
+      dst[((size_t)m * page_size + off) * dv + c] = vx[i];
+    }
+  }
+}
+
+extern "C" int sb_rotate_headnorm_store(const void* proj, int row_width, int dtype, float eps, float q_scale,
+                                        const float* rot_freq, int rot_dims, int interleaved, int head_norm,
+                                        int tie_values, void* q_out, void* cache, const int* block_table,
+                                        int max_pages, const int* token_seq, const int* positions, int num_tokens,
+                                        int H, int G, int d, int dv, int page_size, int num_pages, int write_cache,
+                                        int* err, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (rot_freq == nullptr) rot_dims = 0;
+  const size_t smem = ((size_t)(H + G) * d + rot_dims) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  if (rot_dims % 2 || rot_dims > d || (tie_values && dv != d)) return -4;
+  if (dtype == SB_DTYPE_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(rotate_headnorm_store_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb_launch(rotate_headnorm_store_kernel<float>, num_tokens, 256, smem, stream, (const float*)proj, row_width, eps,
+              q_scale, rot_freq, rot_dims, interleaved, head_norm, tie_values, (float*)q_out, (float*)cache,
+              block_table, max_pages, token_seq, positions, H, G, d, dv, page_size, num_pages, write_cache, err);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(rotate_headnorm_store_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb_launch(rotate_headnorm_store_kernel<bf16>, num_tokens, 256, smem, stream, (const bf16*)proj, row_width, eps,
+              q_scale, rot_freq, rot_dims, interleaved, head_norm, tie_values, (bf16*)q_out, (bf16*)cache,
+              block_table, max_pages, token_seq, positions, H, G, d, dv, page_size, num_pages, write_cache, err);
+  }
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Output gate: x[t, c] *= sigmoid(gate[t, c]), the gate read from a wider row (a column range of
+// the fused projection).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_width, int width) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.y;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
+    const float g = to_f32<T>(gate[(size_t)t * gate_width + c]);
+    const size_t at = (size_t)t * width + c;
+    x[at] = from_f32<T>(to_f32<T>(x[at]) / (1.0f + expf(-g)));
+  }
+}
+
+extern "C" int sb_sigmoid_gate(void* x, const void* gate, int gate_width, int dtype, int num_tokens, int width,
+                               cudaStream_t stream) {
+  if (num_tokens == 0 || width == 0) return 0;
+  for (int t0 = 0; t0 < num_tokens; t0 += 65535) {
+    const dim3 grid((unsigned)min((width + 255) / 256, 64), (unsigned)min(65535, num_tokens - t0));
+    if (dtype == SB_DTYPE_F32)
+      sb_launch(sigmoid_gate_kernel<float>, grid, 256, 0, stream, (float*)x + (size_t)t0 * width,
+                (const float*)gate + (size_t)t0 * gate_width, gate_width, width);
+    else
+      sb_launch(sigmoid_gate_kernel<bf16>, grid, 256, 0, stream, (bf16*)x + (size_t)t0 * width,
+                (const bf16*)gate + (size_t)t0 * gate_width, gate_width, width);
+  }
+  SB_LAUNCH_CHECK();
+  return 0;
+}

@@ -538,8 +538,15 @@ extern "C" int sb_rope_cache_write(const void* qkv, int dtype, const float* cos_
 
 // ---------------------------------------------------------------------------
 // Gated activation: z[t, f] = act(gate_up[t, f]) * gate_up[t, F + f].
-//   act 0: gelu, tanh form; 1: silu; 2: relu.
+//   act 0: gelu, tanh form; 1: silu; 2: relu; 3: the clamped form
+//   z = g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float clamped_gate_value(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+
 __device__ __forceinline__ float apply_activation(float g, int act) {
   if (act == 0) {
     const float c = 0.7978845608028654f;  // sqrt(2 / pi)
@@ -553,7 +560,8 @@ __device__ __forceinline__ float apply_activation(float g, int act) {
 // and division (relative error about 1e-6, far below the rounding of the bfloat16 result).  With
 // the accurate tanh the kernel is bound by instructions, not by memory.
 template <typename T, int ACT>
-__device__ __forceinline__ float gated_value(float g, float u) {
+__device__ __forceinline__ float gated_value(float g, float u, float limit) {
+  if (ACT == 3) return clamped_gate_value(g, u, limit);
   if (ACT == 0 && sizeof(T) == 2) {
     const float c2 = 2.0f * 0.7978845608028654f;
     const float y2 = c2 * (g + 0.044715f * g * g * g);
@@ -565,7 +573,7 @@ __device__ __forceinline__ float gated_value(float g, float u) {
 // One block row per token (blockIdx.y), so that no thread divides.
 template <typename T, int ACT>
 __global__ void __launch_bounds__(256)
-gated_activation_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden) {
+gated_activation_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden, float limit) {
   pdl_wait_block();
   pdl_launch_dependents();
   constexpr int N = Vec<T>::N;
@@ -576,27 +584,29 @@ gated_activation_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ z, in
   Vec<T>::load(row + f, g);
   Vec<T>::load(row + hidden + f, u);
 #pragma unroll
-  for (int k = 0; k < N; ++k) g[k] = gated_value<T, ACT>(g[k], u[k]);
+  for (int k = 0; k < N; ++k) g[k] = gated_value<T, ACT>(g[k], u[k], limit);
   Vec<T>::store(z + (size_t)blockIdx.y * hidden + f, g);
 }
 
 template <typename T>
-static void launch_gated_vec(const T* gate_up, T* z, int num_tokens, int hidden, int act, cudaStream_t stream) {
+static void launch_gated_vec(const T* gate_up, T* z, int num_tokens, int hidden, int act, float limit,
+                             cudaStream_t stream) {
   constexpr int N = Vec<T>::N;
   // (grid.y holds at most 65535 rows: larger steps go in slabs.)
   for (int t0 = 0; t0 < num_tokens; t0 += 65535) {
     const dim3 grid((unsigned)((hidden / N + 255) / 256), (unsigned)min(65535, num_tokens - t0));
     const T* in = gate_up + (size_t)t0 * 2 * hidden;
     T* out = z + (size_t)t0 * hidden;
-    if (act == 0) sb_launch(gated_activation_vec_kernel<T, 0>, grid, 256, 0, stream, in, out, hidden);
-    else if (act == 1) sb_launch(gated_activation_vec_kernel<T, 1>, grid, 256, 0, stream, in, out, hidden);
-    else sb_launch(gated_activation_vec_kernel<T, 2>, grid, 256, 0, stream, in, out, hidden);
+    if (act == 0) sb_launch(gated_activation_vec_kernel<T, 0>, grid, 256, 0, stream, in, out, hidden, limit);
+    else if (act == 1) sb_launch(gated_activation_vec_kernel<T, 1>, grid, 256, 0, stream, in, out, hidden, limit);
+    else if (act == 3) sb_launch(gated_activation_vec_kernel<T, 3>, grid, 256, 0, stream, in, out, hidden, limit);
+    else sb_launch(gated_activation_vec_kernel<T, 2>, grid, 256, 0, stream, in, out, hidden, limit);
   }
 }
 
 template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ z, int hidden, int act,
-                                        size_t n) {
+                                        float limit, size_t n) {
   pdl_wait_block();
   pdl_launch_dependents();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -604,27 +614,27 @@ __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __rest
   const size_t t = i / hidden, f = i - t * hidden;
   const float g = to_f32<T>(gate_up[t * 2 * hidden + f]);
   const float u = to_f32<T>(gate_up[t * 2 * hidden + hidden + f]);
-  z[i] = from_f32<T>(apply_activation(g, act) * u);
+  z[i] = from_f32<T>(act == 3 ? clamped_gate_value(g, u, limit) : apply_activation(g, act) * u);
 }
 
 extern "C" int sb_gated_activation(const void* gate_up, int dtype, void* z, int num_tokens, int hidden, int act,
-                                   cudaStream_t stream) {
+                                   float limit, cudaStream_t stream) {
   const size_t n = (size_t)num_tokens * hidden;
   if (n == 0) return 0;
-  if (act < 0 || act > 2) return -5;
+  if (act < 0 || act > 3) return -5;
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (dtype == SB_DTYPE_F32) {
     if (hidden % 4 == 0)
-      launch_gated_vec<float>((const float*)gate_up, (float*)z, num_tokens, hidden, act, stream);
+      launch_gated_vec<float>((const float*)gate_up, (float*)z, num_tokens, hidden, act, limit, stream);
     else
       sb_launch(gated_activation_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)z,
-          hidden, act, n);
+          hidden, act, limit, n);
   } else {
     if (hidden % 8 == 0)
-      launch_gated_vec<bf16>((const bf16*)gate_up, (bf16*)z, num_tokens, hidden, act, stream);
+      launch_gated_vec<bf16>((const bf16*)gate_up, (bf16*)z, num_tokens, hidden, act, limit, stream);
     else
       sb_launch(gated_activation_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)z,
-          hidden, act, n);
+          hidden, act, limit, n);
   }
   SB_LAUNCH_CHECK();
   return 0;

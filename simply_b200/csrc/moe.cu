@@ -1,0 +1,412 @@
+// Feed-forward layers made of routed experts.  Five kernels, none of which needs the host to
+// know how the tokens were dealt out, so a step can be captured in a CUDA graph:
+//
+//   route    per token: router logits z = W_r x (float32), scores s = softmax(z) (or sigmoid),
+//            the `top` experts with the largest s + correction, weights s * scale (optionally
+//            divided by their sum), and the shared expert's gate sigmoid(w_sg . x)
+//   group    the (token, choice) pairs sorted by expert, cut into tiles of TILE_M rows of one
+//            expert each; experts with index >= E ("identity" experts) take no rows
+//   product  out[r, :] = A[row(r), :] . W[expert of r's tile]^T over those tiles, once with two
+//            sets of weight rows and act(gate) * up on the sums, once plain
+//   combine  y[t] = sum_j weight[t, j] * (expert output of pair (t, j), or x[t] for an identity
+//            expert) + gate[t] * shared[t], summed in the order of j
+//
+// bfloat16 products run on tensor cores (mma.sync through nvcuda::wmma) with float32 sums; the
+// float32 path uses CUDA cores only.  A row's result does not depend on which rows share its tile.
+#include <mma.h>
+
+#include "common.cuh"
+
+#define MOE_TILE_M 64   // rows of a tile
+#define MOE_TILE_N 32   // output columns of one set of weight rows
+
+// ---------------------------------------------------------------------------
+// route: one block per token.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ x, int width, const float* __restrict__ router_w,
+                 const float* __restrict__ correction, const float* __restrict__ shared_gate_w, int NE, int top,
+                 float scale, int score_fn, int renormalize, int* __restrict__ chosen, float* __restrict__ weight,
+                 float* __restrict__ shared_gate) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ float route_smem[];  // x [width], z [NE + 1], choice [NE]
+  float* xs = route_smem;
+  float* z = xs + width;
+  float* choice = z + NE + 1;
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = to_f32<T>(x[(size_t)t * width + c]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int rows = NE + (shared_gate_w != nullptr ? 1 : 0);
+  for (int e = warp; e < rows; e += nwarps) {
+    const float* w = e < NE ? router_w + (size_t)e * width : shared_gate_w;
+    float acc = 0.f;
+    for (int c = lane; c < width; c += 32) acc = fmaf(w[c], xs[c], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  if (shared_gate_w != nullptr && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-z[NE]));
+  if (score_fn == 0) {
+    float m = -INFINITY;
+    for (int e = lane; e < NE; e += 32) m = fmaxf(m, z[e]);
+    m = warp_max(m);
+    float sum = 0.f;
+    for (int e = lane; e < NE; e += 32) sum += expf(z[e] - m);
+    sum = warp_sum(sum);
+    for (int e = lane; e < NE; e += 32) z[e] = expf(z[e] - m) / sum;
+  } else {
+    for (int e = lane; e < NE; e += 32) z[e] = 1.0f / (1.0f + expf(-z[e]));
+  }
+  for (int e = lane; e < NE; e += 32) choice[e] = z[e] + (correction != nullptr ? correction[e] : 0.f);
+  __syncwarp();
+  float total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < NE; e += 32) {
+      const float v = choice[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at >= NE) at = 0;  // (only if every score is NaN)
+    const float s = z[at];
+    total += s;
+    if (lane == 0) {
+      chosen[(size_t)t * top + j] = at;
+      weight[(size_t)t * top + j] = s * scale;
+      choice[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (renormalize && lane == 0)
+    for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] /= total;
+}
+
+extern "C" int sb_moe_route(const void* x, int dtype, int num_tokens, int width, const float* router_w,
+                            const float* correction, const float* shared_gate_w, int NE, int top, float scale,
+                            int score_fn, int renormalize, int* chosen, float* weight, float* shared_gate,
+                            cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  const size_t smem = ((size_t)width + 2 * NE + 1) * sizeof(float);
+  if (top < 1 || top > NE || smem > 200 * 1024) return -13;
+  if (dtype == SB_DTYPE_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb_launch(moe_route_kernel<float>, num_tokens, 128, smem, stream, (const float*)x, width, router_w, correction,
+              shared_gate_w, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    sb_launch(moe_route_kernel<bf16>, num_tokens, 128, smem, stream, (const bf16*)x, width, router_w, correction,
+              shared_gate_w, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
+  }
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// group: one block.  P pairs (pair p = token p / top, choice p % top), E experts with rows.
+//   sorted_pair [P]: the pairs of expert 0, then of expert 1, ... (unused entries at the end: -1)
+//   pos_of_pair [P]: where pair p stands in sorted_pair, or -1 for an identity expert's pair
+//   tile_expert / tile_row0 / tile_rows [max_tiles]: the tiles; unused ones have expert -1
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ chosen, int P, int E, int max_tiles, int* __restrict__ sorted_pair,
+                 int* __restrict__ pos_of_pair, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                 int* __restrict__ tile_rows) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ int group_smem[];  // counts [E], offsets [E], tile_base [E], cursor [E]
+  int* counts = group_smem;
+  int* offsets = counts + E;
+  int* tile_base = offsets + E;
+  int* cursor = tile_base + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = cursor[e] = 0;
+  for (int k = threadIdx.x; k < max_tiles; k += blockDim.x) tile_expert[k] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = chosen[p];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int rows = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = rows;
+      tile_base[e] = tiles;
+      rows += counts[e];
+      tiles += (counts[e] + MOE_TILE_M - 1) / MOE_TILE_M;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int n = counts[e];
+    for (int i = 0, k = tile_base[e]; i < n && k < max_tiles; i += MOE_TILE_M, ++k) {
+      tile_expert[k] = e;
+      tile_row0[k] = offsets[e] + i;
+      tile_rows[k] = min(MOE_TILE_M, n - i);
+    }
+  }
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = chosen[p];
+    int r = -1;
+    if (e >= 0 && e < E) {
+      r = offsets[e] + atomicAdd(&cursor[e], 1);
+      sorted_pair[r] = p;
+    }
+    pos_of_pair[p] = r;
+  }
+}
+
+extern "C" int sb_moe_group(const int* chosen, int P, int E, int max_tiles, int* sorted_pair, int* pos_of_pair,
+                            int* tile_expert, int* tile_row0, int* tile_rows, cudaStream_t stream) {
+  if (P == 0) return 0;
+  const size_t smem = (size_t)4 * (E > 0 ? E : 1) * sizeof(int);
+  if (smem > 48 * 1024) return -13;
+  sb_launch(moe_group_kernel, 1, 1024, smem, stream, chosen, P, E, max_tiles, sorted_pair, pos_of_pair, tile_expert,
+            tile_row0, tile_rows);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// product over the tiles.  Grid (tiles, column tiles).  Row r of a tile reads row
+// `row_pair[r] / pair_div` of A (row_pair null: row r itself) and writes row r of `out`.  A block
+// forms two sets of sums: weight rows n0 + c and `second` + n0 + c (c < 32).  GATED: out[r, n0 + c] =
+// act(set 0) * set 1.  Otherwise the sets are 64 neighbouring output columns (`second` = 32).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float moe_activation(float g, int act) {
+  if (act == 0) {
+    const float c = 0.7978845608028654f;
+    return 0.5f * g * (1.0f + tanhf(c * (g + 0.044715f * g * g * g)));
+  }
+  if (act == 1) return g / (1.0f + expf(-g));
+  return fmaxf(g, 0.f);
+}
+
+// 16 bytes from global memory (16-byte aligned) into a tile row (bfloat16 rows are, float rows are not).
+__device__ __forceinline__ void moe_copy16(bf16* dst, const bf16* src) {
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+}
+__device__ __forceinline__ void moe_copy16(float* dst, const float* src) {
+  const float4 v = *reinterpret_cast<const float4*>(src);
+  dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+}
+
+template <typename T> struct MoeTile;
+template <> struct MoeTile<bf16> { static constexpr int K = 64, LD = 72; };
+template <> struct MoeTile<float> { static constexpr int K = 32, LD = 33; };
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, int pair_div,
+                   const T* __restrict__ W, size_t expert_stride, int second, int K, int N,
+                   const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                   const int* __restrict__ tile_rows, int act, T* __restrict__ out) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  constexpr int BK = MoeTile<T>::K, LD = MoeTile<T>::LD;
+  __shared__ __align__(32) T As[MOE_TILE_M * LD];
+  __shared__ __align__(32) T Ws[2 * MOE_TILE_N * LD];
+  __shared__ __align__(32) float Cs[2 * MOE_TILE_M * (MOE_TILE_N + 4)];
+  __shared__ int src_row[MOE_TILE_M];
+  constexpr int CLD = MOE_TILE_N + 4;
+  const int e = tile_expert[blockIdx.x];
+  if (e < 0) return;
+  const int row0 = tile_row0[blockIdx.x], rows = tile_rows[blockIdx.x];
+  const int n0 = blockIdx.y * (GATED ? MOE_TILE_N : 2 * MOE_TILE_N);
+  const T* We = W + (size_t)e * expert_stride;
+  if (threadIdx.x < MOE_TILE_M) {
+    int r = -1;
+    if ((int)threadIdx.x < rows) r = row_pair != nullptr ? row_pair[row0 + threadIdx.x] / pair_div : row0 + threadIdx.x;
+    src_row[threadIdx.x] = r;
+  }
+  __syncthreads();
+  constexpr int V = 16 / sizeof(T);  // elements of a 16-byte piece
+  const bool vec = K % V == 0;
+
+  [[maybe_unused]] const int warp = threadIdx.x >> 5;
+  // float32: thread (ty, tx) owns rows 4 ty .. 4 ty + 3 and columns 2 tx, 2 tx + 1 of both sets
+  [[maybe_unused]] const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  float acc[2][4][2];
+#pragma unroll
+  for (int s = 0; s < 2; ++s)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[s][i][0] = acc[s][i][1] = 0.f;
+  nvcuda::wmma::fragment<nvcuda::wmma::accumulator, 16, 16, 16, float> cfrag[2];
+  if constexpr (sizeof(T) == 2) {
+    nvcuda::wmma::fill_fragment(cfrag[0], 0.f);
+    nvcuda::wmma::fill_fragment(cfrag[1], 0.f);
+  }
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    // A tile: MOE_TILE_M rows of BK
+    for (int idx = threadIdx.x; idx < MOE_TILE_M * (BK / V); idx += blockDim.x) {
+      const int r = idx / (BK / V), c = (idx - r * (BK / V)) * V;
+      const int src = src_row[r];
+      T* dst = As + r * LD + c;
+      if (src >= 0 && vec && k0 + c + V <= K) {
+        moe_copy16(dst, A + (size_t)src * K + k0 + c);
+      } else {
+#pragma unroll
+        for (int q = 0; q < V; ++q)
+          dst[q] = (src >= 0 && k0 + c + q < K) ? A[(size_t)src * K + k0 + c + q] : from_f32<T>(0.f);
+      }
+    }
+    // W tiles: two sets of MOE_TILE_N rows of BK
+    for (int idx = threadIdx.x; idx < 2 * MOE_TILE_N * (BK / V); idx += blockDim.x) {
+      const int j = idx / (BK / V), c = (idx - j * (BK / V)) * V;
+      const int s = j / MOE_TILE_N, jj = j - s * MOE_TILE_N;
+      const int n = n0 + (GATED ? 0 : s * MOE_TILE_N) + jj;  // output column
+      const int wrow = n < N ? (GATED ? s * second + n : n) : -1;
+      T* dst = Ws + j * LD + c;
+      if (wrow >= 0 && vec && k0 + c + V <= K) {
+        moe_copy16(dst, We + (size_t)wrow * K + k0 + c);
+      } else {
+#pragma unroll
+        for (int q = 0; q < V; ++q)
+          dst[q] = (wrow >= 0 && k0 + c + q < K) ? We[(size_t)wrow * K + k0 + c + q] : from_f32<T>(0.f);
+      }
+    }
+    __syncthreads();
+    if constexpr (sizeof(T) == 2) {
+      using namespace nvcuda;
+      const int wr = warp & 3, wc = warp >> 2;
+#pragma unroll
+      for (int kk = 0; kk < BK; kk += 16) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+        wmma::load_matrix_sync(a, reinterpret_cast<const bf16*>(As) + wr * 16 * LD + kk, LD);
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b;
+          wmma::load_matrix_sync(b, reinterpret_cast<const bf16*>(Ws) + (s * MOE_TILE_N + wc * 16) * LD + kk, LD);
+          wmma::mma_sync(cfrag[s], a, b, cfrag[s]);
+        }
+      }
+    } else {
+      const float* Af = reinterpret_cast<const float*>(As);
+      const float* Wf = reinterpret_cast<const float*>(Ws);
+#pragma unroll 8
+      for (int kk = 0; kk < BK; ++kk) {
+        float a[4], b[2][2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = Af[(ty * 4 + i) * LD + kk];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          b[s][0] = Wf[(s * MOE_TILE_N + tx * 2) * LD + kk];
+          b[s][1] = Wf[(s * MOE_TILE_N + tx * 2 + 1) * LD + kk];
+        }
+#pragma unroll
+        for (int s = 0; s < 2; ++s)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[s][i][0] = fmaf(a[i], b[s][0], acc[s][i][0]);
+            acc[s][i][1] = fmaf(a[i], b[s][1], acc[s][i][1]);
+          }
+      }
+    }
+    __syncthreads();
+  }
+  if constexpr (sizeof(T) == 2) {
+    const int wr = warp & 3, wc = warp >> 2;
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+      nvcuda::wmma::store_matrix_sync(Cs + (s * MOE_TILE_M + wr * 16) * CLD + wc * 16, cfrag[s], CLD,
+                                      nvcuda::wmma::mem_row_major);
+  } else {
+#pragma unroll
+    for (int s = 0; s < 2; ++s)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        Cs[(s * MOE_TILE_M + ty * 4 + i) * CLD + tx * 2] = acc[s][i][0];
+        Cs[(s * MOE_TILE_M + ty * 4 + i) * CLD + tx * 2 + 1] = acc[s][i][1];
+      }
+  }
+  __syncthreads();
+  if (GATED) {
+    for (int idx = threadIdx.x; idx < rows * MOE_TILE_N; idx += blockDim.x) {
+      const int r = idx / MOE_TILE_N, c = idx - r * MOE_TILE_N;
+      if (n0 + c < N)
+        out[(size_t)(row0 + r) * N + n0 + c] =
+            from_f32<T>(moe_activation(Cs[r * CLD + c], act) * Cs[(MOE_TILE_M + r) * CLD + c]);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < rows * 2 * MOE_TILE_N; idx += blockDim.x) {
+      const int r = idx / (2 * MOE_TILE_N), c = idx - r * 2 * MOE_TILE_N;
+      const int s = c / MOE_TILE_N, cc = c - s * MOE_TILE_N;
+      if (n0 + c < N) out[(size_t)(row0 + r) * N + n0 + c] = from_f32<T>(Cs[(s * MOE_TILE_M + r) * CLD + cc]);
+    }
+  }
+}
+
+// gated = 1: W [E, 2 N, K] (gate rows, then up rows), out [P, N] = act(gate) * up;
+// gated = 0: W [E, N, K], out [P, N].
+extern "C" int sb_moe_product(const void* A, const int* row_pair, int pair_div, const void* W, int dtype, int gated,
+                              int K, int N, const int* tile_expert, const int* tile_row0, const int* tile_rows,
+                              int max_tiles, int act, void* out, cudaStream_t stream) {
+  if (max_tiles == 0 || N == 0) return 0;
+  if (K <= 0 || act < 0 || act > 2 || pair_div < 1) return -13;
+  const size_t stride = (size_t)(gated ? 2 : 1) * N * K;
+  const int per_block = gated ? MOE_TILE_N : 2 * MOE_TILE_N;
+  const dim3 grid(max_tiles, (N + per_block - 1) / per_block);
+#define SB_MOE_PRODUCT(T_, G_)                                                                                  \
+  sb_launch(moe_product_kernel<T_, G_>, grid, 256, 0, stream, (const T_*)A, row_pair, pair_div, (const T_*)W,   \
+            stride, G_ ? N : MOE_TILE_N, K, N, tile_expert, tile_row0, tile_rows, act, (T_*)out)
+  if (dtype == SB_DTYPE_F32) {
+    if (gated) SB_MOE_PRODUCT(float, true);
+    else SB_MOE_PRODUCT(float, false);
+  } else {
+    if (gated) SB_MOE_PRODUCT(bf16, true);
+    else SB_MOE_PRODUCT(bf16, false);
+  }
+#undef SB_MOE_PRODUCT
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// combine: one block per token.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const T* __restrict__ x, const T* __restrict__ y_pair, const int* __restrict__ chosen,
+                   const float* __restrict__ weight, const int* __restrict__ pos_of_pair,
+                   const T* __restrict__ shared, const float* __restrict__ shared_gate, int E, int top, int width,
+                   T* __restrict__ out) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const float sg = shared == nullptr ? 0.f : (shared_gate != nullptr ? shared_gate[t] : 1.0f);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < top; ++j) {
+      const int p = t * top + j;
+      const int pos = pos_of_pair[p];
+      const float v = pos >= 0 ? to_f32<T>(y_pair[(size_t)pos * width + c]) : to_f32<T>(x[(size_t)t * width + c]);
+      acc = fmaf(weight[p], v, acc);
+    }
+    if (shared != nullptr) acc = fmaf(sg, to_f32<T>(shared[(size_t)t * width + c]), acc);
+    out[(size_t)t * width + c] = from_f32<T>(acc);
+  }
+}
+
+extern "C" int sb_moe_combine(const void* x, const void* y_pair, int dtype, const int* chosen, const float* weight,
+                              const int* pos_of_pair, const void* shared, const float* shared_gate, int E, int top,
+                              int num_tokens, int width, void* out, cudaStream_t stream) {
+  if (num_tokens == 0) return 0;
+  if (dtype == SB_DTYPE_F32)
+    sb_launch(moe_combine_kernel<float>, num_tokens, 256, 0, stream, (const float*)x, (const float*)y_pair, chosen,
+              weight, pos_of_pair, (const float*)shared, shared_gate, E, top, width, (float*)out);
+  else
+    sb_launch(moe_combine_kernel<bf16>, num_tokens, 256, 0, stream, (const bf16*)x, (const bf16*)y_pair, chosen,
+              weight, pos_of_pair, (const bf16*)shared, shared_gate, E, top, width, (bf16*)out);
+  SB_LAUNCH_CHECK();
+  return 0;
+}

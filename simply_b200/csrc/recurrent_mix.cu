@@ -1,5 +1,5 @@
-// Kernels of the recurrent mixers: the gated delta rule with its short convolutions, and the
-// mean of RMS-normed branches.  Everything here computes in float32; T is the storage type of
+// Kernels of the recurrent mixers: the gated delta rule with its short convolutions, the
+// forget-gate recurrence, and the mean of RMS-normed branches.  Everything here computes in float32; T is the storage type of
 // the activations that come in from and go out to matrix products.
 //
 //   inputs    y_c[t] = silu(sum_j w[c, j] x_c[t - (taps-1) + j])   x before the request's start is
@@ -423,8 +423,142 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
 }
 
 // ---------------------------------------------------------------------------
-// Output of the delta rule: per head RMS norm, channel scale, gate.  One block per token, a warp
-// per head.
+// The forget-gate recurrence (HGRN2): per head a matrix S [d, dv] whose rows decay by f and take in
+// (1 - f) v, read by q after the write:
+//   q = silu(pq),  f = l + (1 - l) sigmoid(pf + b),  S <- diag(f) S + (1 - f) v^T,  o = S^T q
+// `pre` [T, row_width] holds pq (H d) | pf (H d) | v (H dv) as the projection left them; the
+// activations and the gate are computed here, in float32, as a chunk of tokens is fetched.  The
+// layout of a block is the delta rule's: a column of S over RS neighbouring lanes with ROWS rows
+// each, a block per (head, sequence, tile of columns), the state written back by the slot's first row.
+// ---------------------------------------------------------------------------
+#define FORGET_CHUNK 16
+
+template <typename T, int RS, int ROWS>
+__global__ void __launch_bounds__(128)
+forget_scan_kernel(const T* __restrict__ pre, int row_width, const float* __restrict__ bias,
+                   const float* __restrict__ lower, float* __restrict__ state, const int* __restrict__ cu_q,
+                   const int* __restrict__ slots, int num_slots, int H, int d, int dv, int cols,
+                   float* __restrict__ out, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) float stage[];  // q [CHUNK][d], f [CHUNK][d], v [CHUNK][cols]
+  const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
+  const int rs = threadIdx.x % RS, col_local = threadIdx.x / RS;
+  const int col = col0 + col_local;
+  const bool on = col_local < cols && col < dv;
+  const int first = cu_q[b], n = cu_q[b + 1] - first;
+  const int slot = slots[b];
+  if (slot < 0 || slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
+    return;
+  }
+  float* sq = stage;
+  float* sf = sq + FORGET_CHUNK * d;
+  float* sv = sf + FORGET_CHUNK * d;
+  const int q_at = h * d, f_at = H * d + h * d, v_at = 2 * H * d + h * dv;
+  float* S = state + ((size_t)slot * H + h) * d * dv;
+  float s[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int row = rs + RS * r;
+    s[r] = (on && row < d) ? S[(size_t)row * dv + col] : 0.f;
+  }
+  for (int base = 0; base < n; base += FORGET_CHUNK) {
+    const int count = min(FORGET_CHUNK, n - base);
+    __syncthreads();  // the walk over the chunk before is over
+    for (int idx = threadIdx.x; idx < count * d; idx += blockDim.x) {
+      const int i = idx / d, c = idx - i * d;
+      const T* x = pre + (size_t)(first + base + i) * row_width;
+      const float pq = to_f32<T>(x[q_at + c]);
+      const float pf = to_f32<T>(x[f_at + c]) + bias[q_at + c];
+      const float l = lower[q_at + c];
+      sq[idx] = pq * sigmoid_f32(pq);
+      sf[idx] = l + (1.0f - l) * sigmoid_f32(pf);
+    }
+    for (int idx = threadIdx.x; idx < count * cols; idx += blockDim.x) {
+      const int i = idx / cols, c = idx - i * cols;
+      sv[idx] = to_f32<T>(pre[(size_t)(first + base + i) * row_width + v_at + min(col0 + c, dv - 1)]);
+    }
+    __syncthreads();
+    for (int i = 0; i < count; ++i) {
+      const float* qq = sq + i * d;
+      const float* ff = sf + i * d;
+      const float vv = sv[i * cols + min(col_local, cols - 1)];
+      float od = 0.f;
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        const int row = rs + RS * r;
+        if (row < d) {
+          const float f = ff[row];
+          s[r] = fmaf(f, s[r], (1.0f - f) * vv);
+          od = fmaf(s[r], qq[row], od);
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < RS; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
+      if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = od;
+    }
+  }
+  if (on && first_row_of_slot(slots, b)) {
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const int row = rs + RS * r;
+      if (row < d) S[(size_t)row * dv + col] = s[r];
+    }
+  }
+}
+
+extern "C" int sb_forget_scan(const void* pre, int row_width, int dtype, const float* bias, const float* lower,
+                              float* state, const int* cu_q, const int* slots, int num_seqs, int num_slots, int H,
+                              int d, int dv, int max_q_len, float* out, int* err, cudaStream_t stream) {
+  if (num_seqs == 0) return 0;
+  if (d <= 0 || d > 32 * 32 || dv <= 0 || H <= 0) return -13;
+  const int rows = d <= 8 * 32 ? 8 : 32;
+  int rs = 1;
+  while (rs * rows < d) rs <<= 1;
+  const int threads = max_q_len >= 64 ? 128 : 64;
+  int cols = threads / rs;
+  if (cols < 1) cols = 1;
+  if (cols > dv) cols = dv;
+  const int block = ((cols * rs + 31) / 32) * 32;
+  const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
+  const size_t smem = (size_t)FORGET_CHUNK * (2 * d + cols) * sizeof(float);
+  if (smem > 200 * 1024) return -13;
+#define SB_FORGET_V(T_, RS_, ROWS_)                                                                            \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      cudaFuncSetAttribute(forget_scan_kernel<T_, RS_, ROWS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                           (int)smem);                                                                         \
+    sb_launch(forget_scan_kernel<T_, RS_, ROWS_>, grid, block, smem, stream, (const T_*)pre, row_width, bias,  \
+              lower, state, cu_q, slots, num_slots, H, d, dv, cols, out, err);                                 \
+  } while (0)
+#define SB_FORGET(RS_)                                      \
+  do {                                                      \
+    if (dtype == SB_DTYPE_F32) {                            \
+      if (rows == 8) SB_FORGET_V(float, RS_, 8);            \
+      else SB_FORGET_V(float, RS_, 32);                     \
+    } else {                                                \
+      if (rows == 8) SB_FORGET_V(bf16, RS_, 8);             \
+      else SB_FORGET_V(bf16, RS_, 32);                      \
+    }                                                       \
+  } while (0)
+  switch (rs) {
+    case 1: SB_FORGET(1); break;
+    case 2: SB_FORGET(2); break;
+    case 4: SB_FORGET(4); break;
+    case 8: SB_FORGET(8); break;
+    case 16: SB_FORGET(16); break;
+    default: SB_FORGET(32); break;
+  }
+#undef SB_FORGET
+#undef SB_FORGET_V
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Output of a recurrent mixer: per head RMS norm, channel scale, and (gate_offset >= 0) a gate read
+// from `low`.  One block per token, a warp per head.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -440,7 +574,8 @@ gated_head_norm_kernel(const float* __restrict__ o, const T* __restrict__ low, i
     ss = warp_sum(ss);
     const float rstd = 1.0f / sqrtf(ss / (float)dv + eps);
     for (int c = lane; c < dv; c += 32) {
-      const float gate = sigmoid_f32(to_f32<T>(low[(size_t)t * low_width + gate_offset + h * dv + c]));
+      const float gate = gate_offset < 0 ? 1.0f
+          : sigmoid_f32(to_f32<T>(low[(size_t)t * low_width + gate_offset + h * dv + c]));
       out[((size_t)t * H + h) * dv + c] = from_f32<T>(src[c] * rstd * w[c] * gate);
     }
   }

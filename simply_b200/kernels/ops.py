@@ -227,7 +227,7 @@ class CudaOps:
         "sb_rotation_tables": [c_void, c_void, c_float, c_void, c_void, c_int, c_int, c_void],
         "sb_rope_cache_write": [c_void, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int, c_void,
                                 c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void],
-        "sb_gated_activation": [c_void, c_int, c_void, c_int, c_int, c_int, c_void],
+        "sb_gated_activation": [c_void, c_int, c_void, c_int, c_int, c_int, c_float, c_void],
         "sb_soft_cap": [c_void, c_float, c_ll, c_void],
         "sb_gemm_f32_nt": [c_void, c_void, c_void, c_int, c_int, c_int, c_float, c_void],
         "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void],
@@ -258,6 +258,19 @@ class CudaOps:
                                c_void],
         "sb_normed_mean": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_float,
                            c_int, c_int, c_void, c_void],
+        "sb_rotate_headnorm_store": [c_void, c_int, c_int, c_float, c_float, c_void, c_int, c_int, c_int, c_int,
+                                     c_void, c_void, c_void, c_int, c_void, c_void, c_int, c_int, c_int, c_int,
+                                     c_int, c_int, c_int, c_int, c_void, c_void],
+        "sb_sigmoid_gate": [c_void, c_void, c_int, c_int, c_int, c_int, c_void],
+        "sb_forget_scan": [c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_void, c_void, c_void],
+        "sb_moe_route": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_int, c_int, c_float, c_int, c_int,
+                         c_void, c_void, c_void, c_void],
+        "sb_moe_group": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void],
+        "sb_moe_product": [c_void, c_void, c_int, c_void, c_int, c_int, c_int, c_int, c_void, c_void, c_void, c_int,
+                           c_int, c_void, c_void],
+        "sb_moe_combine": [c_void, c_void, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
+                           c_void, c_void],
         "sb_sample": [c_void, c_void, c_void, c_int, c_int, c_void, c_void],
         "sb_sample_logprobs": [c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_void, c_void],
         "sb_decode_advance": [c_void, c_void, c_void, c_void, c_void, c_void, c_void, c_int, c_void],
@@ -613,10 +626,13 @@ class CudaOps:
         return out
     return torch.mm(x, w.t())
 
-  def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor, activation: int) -> torch.Tensor:
-    """act(x . w_gate^T) * (x . w_up^T) with w_gate_up = [gate rows; up rows]: [M, N/2]."""
+  def gated_linear(self, x: torch.Tensor, w_gate_up: torch.Tensor, activation: int, limit: float = 0.0) -> torch.Tensor:
+    """act(x . w_gate^T) * (x . w_up^T) with w_gate_up = [gate rows; up rows]: [M, N/2].  Activation 3
+    (clamped) takes `limit` and acts on both halves (csrc/elementwise.cu)."""
     m, k = x.shape
     n = w_gate_up.shape[0]
+    if activation == 3:
+      return self.gated_activation(self.linear(x, w_gate_up), activation, limit)
     if w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and m <= self.skinny_max_rows:
       out = self._new(m, n // 2, dtype=torch.bfloat16)
       if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n, k, 2, 0.0,
@@ -668,10 +684,11 @@ class CudaOps:
                  float(cap), 0, self.skinny_warps)
     return out
 
-  def gated_activation(self, gate_up: torch.Tensor, activation: int) -> torch.Tensor:
+  def gated_activation(self, gate_up: torch.Tensor, activation: int, limit: float = 0.0) -> torch.Tensor:
     t, two_f = gate_up.shape
     out = self._new(t, two_f // 2, dtype=gate_up.dtype)
-    self._call("sb_gated_activation", _ptr(gate_up), _code(gate_up), _ptr(out), t, two_f // 2, activation)
+    self._call("sb_gated_activation", _ptr(gate_up), _code(gate_up), _ptr(out), t, two_f // 2, activation,
+               float(limit))
     return out
 
   # ---- norms ----------------------------------------------------------------
@@ -908,6 +925,93 @@ class CudaOps:
                x.shape[0], num_heads, dim, _ptr(out))
     return out
 
+  # ---- attention with heads normed one by one ----------------------------------
+  def rotate_headnorm_store(self, proj: torch.Tensor, eps: float, q_scale: float, rot_freq: torch.Tensor | None, *,
+                            interleaved: bool, head_norm: bool, tie_values: bool, num_heads: int, num_kv_heads: int,
+                            head_dim: int, storage: torch.Tensor | None, block_table: torch.Tensor,
+                            ctx: Any) -> torch.Tensor:
+    """proj [T, q | k | (v) | ...] -> queries [T, num_heads, head_dim], rotated, each head divided by
+    its root mean square, times `q_scale`; keys (rotated, normed) and values (the keys as projected
+    when `tie_values`, else the v columns) go into the pages of `storage` (csrc/attention_prepare.cu)."""
+    t = proj.shape[0]
+    q = self._new(t, num_heads, head_dim, dtype=proj.dtype)
+    if storage is not None and storage.dtype != proj.dtype:
+      raise KernelError("cache and activations must share one dtype")
+    self._call("sb_rotate_headnorm_store", _ptr(proj), proj.shape[1], _code(proj), float(eps), float(q_scale),
+               _ptr(rot_freq), 2 * rot_freq.numel() if rot_freq is not None else 0, int(interleaved), int(head_norm),
+               int(tie_values), _ptr(q), _ptr(storage), _ptr(block_table), block_table.shape[1],
+               _ptr(ctx.token_seq), _ptr(ctx.positions), t, num_heads, num_kv_heads, head_dim, head_dim,
+               ctx.page_size, storage.shape[0] if storage is not None else 0, int(storage is not None),
+               _ptr(self.err))
+    return q
+
+  def sigmoid_gate(self, x: torch.Tensor, proj: torch.Tensor, offset: int) -> torch.Tensor:
+    """x [T, N] *= sigmoid(proj[:, offset : offset + N]), in place."""
+    gate = proj[:, offset:]
+    self._call("sb_sigmoid_gate", _ptr(x), gate.data_ptr(), proj.shape[1], _code(x), x.shape[0], x.shape[1])
+    return x
+
+  # ---- forget-gate recurrence ---------------------------------------------------
+  def forget_gate_scan(self, pre: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor,
+                       ctx: Any, *, num_heads: int, head_dim: int, value_dim: int) -> torch.Tensor:
+    """pre [T, q | f | v] as projected -> float32 o [T, heads, value_dim]; walks every sequence's
+    tokens through its state [slots, heads, head_dim, value_dim] (csrc/recurrent_mix.cu)."""
+    out = self._new(pre.shape[0], num_heads, value_dim, dtype=torch.float32)
+    self._call("sb_forget_scan", _ptr(pre), pre.shape[1], _code(pre), _ptr(bias), _ptr(lower), _ptr(state),
+               _ptr(ctx.cu_q), _ptr(ctx.slots), ctx.num_seqs, state.shape[0], num_heads, head_dim, value_dim,
+               ctx.max_q_len, _ptr(out), _ptr(self.err))
+    return out
+
+  # ---- routed experts -------------------------------------------------------------
+  MOE_TILE_ROWS = 64  # rows of a tile of the experts' products (csrc/moe.cu)
+
+  def route_tokens(self, x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None,
+                   shared_gate_w: torch.Tensor | None, *, top: int, scale: float, score: int = 0,
+                   renormalize: bool = False):
+    """Per token the `top` chosen experts (int32 [T, top]), their weights (float32 [T, top]) and the
+    shared expert's gate (float32 [T], or None)."""
+    t, width = x.shape
+    chosen = self._new(t, top, dtype=torch.int32)
+    weight = self._new(t, top, dtype=torch.float32)
+    gate = self._new(t, dtype=torch.float32) if shared_gate_w is not None else None
+    self._call("sb_moe_route", _ptr(x), _code(x), t, width, _ptr(router), _ptr(correction), _ptr(shared_gate_w),
+               router.shape[0], top, float(scale), int(score), int(renormalize), _ptr(chosen), _ptr(weight), _ptr(gate))
+    return chosen, weight, gate
+
+  def mix_experts(self, x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, gate_up: torch.Tensor | None,
+                  down: torch.Tensor | None, num_experts: int, activation: int, shared: torch.Tensor | None,
+                  shared_gate: torch.Tensor | None) -> torch.Tensor:
+    """sum_j weight[t, j] * expert(chosen[t, j])(x[t]) + shared_gate[t] * shared[t]; experts with an
+    index >= num_experts return their input.  gate_up [E, 2F, W], down [E, W, F]."""
+    t, width = x.shape
+    top = chosen.shape[1]
+    pairs = t * top
+    out = self._new(t, width, dtype=x.dtype)
+    pos = self._new(pairs, dtype=torch.int32)
+    y_pair = None
+    if num_experts > 0:
+      if gate_up.dtype != x.dtype:
+        raise KernelError("the experts' matrices and the activations must share one dtype")
+      max_tiles = pairs // self.MOE_TILE_ROWS + min(num_experts, pairs)
+      words = self._new(pairs + 3 * max_tiles, dtype=torch.int32)
+      sorted_pair, tiles = words[:pairs], words[pairs:].view(3, max_tiles)
+      self._call("sb_moe_group", _ptr(chosen), pairs, num_experts, max_tiles, _ptr(sorted_pair), _ptr(pos),
+                 _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]))
+      hidden = down.shape[2]
+      h = self._new(pairs, hidden, dtype=x.dtype)
+      self._call("sb_moe_product", _ptr(x), _ptr(sorted_pair), top, _ptr(gate_up), _code(x), 1, width, hidden,
+                 _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, activation, _ptr(h))
+      y_pair = self._new(pairs, width, dtype=x.dtype)
+      self._call("sb_moe_product", _ptr(h), None, 1, _ptr(down), _code(x), 0, hidden, width,
+                 _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, 0, _ptr(y_pair))
+    else:
+      pos.fill_(-1)
+    if shared is not None and shared.dtype != x.dtype:
+      shared = self.cast(shared, x.dtype)
+    self._call("sb_moe_combine", _ptr(x), _ptr(y_pair), _code(x), _ptr(chosen), _ptr(weight), _ptr(pos), _ptr(shared),
+               _ptr(shared_gate), num_experts, top, t, width, _ptr(out))
+    return out
+
   # ---- gated delta rule -------------------------------------------------------
   def delta_rule_inputs(self, pre: torch.Tensor, low: torch.Tensor, conv_weight: torch.Tensor,
                         conv_state: torch.Tensor, decay_bias: torch.Tensor, neg_rate: torch.Tensor, ctx: Any, *,
@@ -937,8 +1041,14 @@ class CudaOps:
                ctx.max_q_len, _ptr(out), _ptr(self.err))
     return out
 
-  def gated_head_norm(self, o: torch.Tensor, low: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float,
-                      num_heads: int, value_dim: int) -> torch.Tensor:
+  def gated_head_norm(self, o: torch.Tensor, low: torch.Tensor | None, gate_offset: int, weight: torch.Tensor,
+                      eps: float, num_heads: int, value_dim: int) -> torch.Tensor:
+    """Per head o / rms(o) * weight, times sigmoid(low[:, gate_offset + ...]); `low` None: no gate."""
+    if low is None:
+      out = self._new(o.shape[0], num_heads * value_dim)
+      self._call("sb_gated_head_norm", _ptr(o), None, 0, -1, _code(out), _ptr(weight),
+                 float(eps), o.shape[0], num_heads, value_dim, _ptr(out))
+      return out
     out = self._new(o.shape[0], num_heads * value_dim, dtype=low.dtype)
     self._call("sb_gated_head_norm", _ptr(o), _ptr(low), low.shape[1], gate_offset, _code(low), _ptr(weight),
                float(eps), o.shape[0], num_heads, value_dim, _ptr(out))

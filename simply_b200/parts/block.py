@@ -10,6 +10,8 @@ is read and written once per branch.
 (simply/model_lib.py:2659-2708; simply/config_lib.py:868-870):
   h += post_mixer_norm(mixer(pre_mixer_norm(h)))
   h += post_ff_norm(feed_forward(pre_ff_norm(h)))
+With `residual_scale` = m both branches are added times m (folded into the post norms' scales),
+and a layer without a feed-forward has only the first line.
 `pre_norm` is the same without post norms (use_post_ln=False).
 `parallel_residual` has one norm whose output both sublayers read:
   h += mixer(norm(h)) + feed_forward(norm(h))
@@ -45,6 +47,15 @@ class ResidualStream:
       return
     self.flush(ctx)
     self._branch, self._post = branch, post_norm
+
+  def add_input(self, x: torch.Tensor, ctx: Any) -> None:
+    """Adds `x` as it is: in the activation dtype it rides along with what is pending, in float32
+    (when the activation dtype would round it) it is added at once."""
+    if x.dtype == self.h.dtype and x.dtype != ctx.ops.dtype:
+      self.flush(ctx)
+      ctx.ops.add_to_residual(self.h, x)
+    else:
+      self.add(x, None, ctx)
 
   def flush(self, ctx: Any) -> None:
     if self._branch is not None:
@@ -87,18 +98,24 @@ class SandwichNormBlock(Block):
   uses_post_norms = True
 
   def __init__(self, prefix: str, width: int, norm: PartSpec, mixer: Mixer, feed_forward: FeedForward,
-               names: dict[str, str] | None = None):
+               names: dict[str, str] | None = None, residual_scale: float = 1.0, full_names: bool = False):
     self.prefix = prefix
     self.mixer = mixer
-    self.feed_forward = feed_forward
+    self.feed_forward = None if isinstance(feed_forward, NoFeedForward) else feed_forward
+    self.residual_scale = float(residual_scale)
+    if self.residual_scale != 1.0 and not self.uses_post_norms:
+      raise ValueError(f"{prefix}: a residual scale needs post norms to carry it")
     names = names or {}
     def make(role: str) -> Norm:
-      return build_part(NORMS, PartSpec(norm.kind, f"{prefix}.{names.get(role, role)}",
-                                        {"width": width, **norm.params}))
+      params = {"width": width, **norm.params}
+      if full_names:  # `names` gives the scale's whole name after the layer's prefix
+        params["name"] = f"{prefix}.{names.get(role, role)}"
+      return build_part(NORMS, PartSpec(norm.kind, f"{prefix}.{names.get(role, role)}", params))
+    has_ff = self.feed_forward is not None
     self.pre_mixer = make("pre_mixer")
-    self.pre_feed_forward = make("pre_feed_forward")
+    self.pre_feed_forward = make("pre_feed_forward") if has_ff else None
     self.post_mixer = make("post_mixer") if self.uses_post_norms else None
-    self.post_feed_forward = make("post_feed_forward") if self.uses_post_norms else None
+    self.post_feed_forward = make("post_feed_forward") if self.uses_post_norms and has_ff else None
 
   def _norms(self) -> list[Norm]:
     return [n for n in (self.pre_mixer, self.post_mixer, self.pre_feed_forward,
@@ -109,24 +126,34 @@ class SandwichNormBlock(Block):
 
   @property
   def graph_safe(self) -> bool:
-    return (self.mixer.graph_safe and self.feed_forward.graph_safe
+    return (self.mixer.graph_safe and (self.feed_forward is None or self.feed_forward.graph_safe)
             and all(n.graph_safe for n in self._norms()))
 
   def tensor_specs(self) -> list[TensorSpec]:
-    specs = self.mixer.tensor_specs() + self.feed_forward.tensor_specs()
+    specs = self.mixer.tensor_specs() + (self.feed_forward.tensor_specs() if self.feed_forward is not None else [])
     for n in self._norms():
       specs += n.tensor_specs()
     return specs
 
   def bind(self, tensors, ops) -> None:
     self.mixer.bind(tensors, ops)
-    self.feed_forward.bind(tensors, ops)
+    if self.feed_forward is not None:
+      self.feed_forward.bind(tensors, ops)
     for n in self._norms():
       n.bind(tensors, ops)
+    if self.residual_scale != 1.0:
+      # m * (x / rms(x) * w) = x / rms(x) * (m w): the branch's factor lives in the post norm's
+      # scale, in float32 (with a scale applied as 1 + w: 1 + w' = m (1 + w)).
+      for n in (self.post_mixer, self.post_feed_forward):
+        if n is not None:
+          w = n.weight.float()
+          n.weight = ((w + 1.0) * self.residual_scale - 1.0 if n.plus_one else w * self.residual_scale).contiguous()
 
   def forward(self, stream: ResidualStream, ctx: Any, cache: Any, writes_cache: bool = True) -> None:
     y = stream.normed(self.pre_mixer, ctx)
     stream.add(self.mixer.forward(y, ctx, cache, writes_cache), self.post_mixer, ctx)
+    if self.feed_forward is None:
+      return
     y = stream.normed(self.pre_feed_forward, ctx)
     stream.add(self.feed_forward.forward(y, ctx), self.post_feed_forward, ctx)
 

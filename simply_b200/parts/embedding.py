@@ -40,6 +40,10 @@ class TokenEmbedding(Embedding):
     """float32 [T, width]: the start of the residual stream."""
     return ctx.ops.embed(self.table, ctx.token_ids, self.scale)
 
+  def rides_exactly(self, dtype: torch.dtype) -> bool:
+    """True if `forward`'s float32 rows are exact in `dtype` (rows of the table as they are)."""
+    return dtype == torch.float32 or (self.scale == 1.0 and self.table is not None and self.table.dtype == dtype)
+
 
 @HEADS.register("tied_head")
 class TiedHead(Head):

@@ -3,7 +3,8 @@
 simply/model_lib.py:714-730 with use_gated_activation_in_ffn: the activation
 acts on the gate projection (`ffn_0_gate`), the product with `ffn_0` (up) feeds
 `ffn_1` (down).  The activation is chosen by name; `gelu_tanh` is
-simply/model_lib.py:93-96.
+simply/model_lib.py:93-96.  `clamped_swish` takes a `limit` L and acts on both halves:
+g' = min(g, L), u' = clamp(u, -L, L), z = g' sigmoid(1.702 g') (u' + 1).
 """
 
 from __future__ import annotations
@@ -21,6 +22,7 @@ from simply_b200.weights.loader import TensorSpec
 ACTIVATIONS.register("gelu_tanh", 0)
 ACTIVATIONS.register("silu", 1)
 ACTIVATIONS.register("relu", 2)
+ACTIVATIONS.register("clamped_swish", 3)
 
 
 @FEED_FORWARDS.register("gated")
@@ -29,11 +31,14 @@ class GatedFeedForward(FeedForward):
   graph_safe = True
 
   def __init__(self, prefix: str, width: int, hidden: int, activation: str,
-               names: dict[str, str] | None = None):
+               names: dict[str, str] | None = None, limit: float = 0.0):
     self.prefix = prefix
     self.width = width
     self.hidden = hidden
     self.activation = ACTIVATIONS.get(activation)
+    self.limit = float(limit)
+    if activation == "clamped_swish" and not self.limit > 0:
+      raise ValueError(f"{prefix}: the clamped activation needs a positive limit")
     names = names or {}  # role -> the tensor's name after the prefix
     self.gate_proj = Linear(f"{prefix}.{names.get('gate', 'gate_proj.weight')}", hidden, width)
     self.up_proj = Linear(f"{prefix}.{names.get('up', 'up_proj.weight')}", hidden, width)
@@ -50,7 +55,10 @@ class GatedFeedForward(FeedForward):
 
   def forward(self, x: torch.Tensor, ctx: Any) -> torch.Tensor:
     ops = ctx.ops
-    z = ops.gated_linear(x, self.gate_up_weight, self.activation)
+    if self.limit:
+      z = ops.gated_linear(x, self.gate_up_weight, self.activation, limit=self.limit)
+    else:
+      z = ops.gated_linear(x, self.gate_up_weight, self.activation)
     return self.down_proj(z, ctx)
 
 

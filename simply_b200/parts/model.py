@@ -23,6 +23,9 @@ from simply_b200.weights.loader import TensorSpec
 # Importing the part modules registers the built-in parts.
 from simply_b200.parts import attention as _attention  # noqa: F401
 from simply_b200.parts import delta_rule as _delta_rule  # noqa: F401
+from simply_b200.parts import experts as _experts  # noqa: F401
+from simply_b200.parts import forget_gate as _forget_gate  # noqa: F401
+from simply_b200.parts import head_norm_attention as _head_norm_attention  # noqa: F401
 from simply_b200.parts import normed_attention as _normed_attention  # noqa: F401
 from simply_b200.parts import embedding as _embedding  # noqa: F401
 from simply_b200.parts import feedforward as _feedforward  # noqa: F401
@@ -98,9 +101,24 @@ class DecoderModel:
   # ---- forward --------------------------------------------------------------
   def forward(self, ctx: Any, caches: dict[str, Any]) -> torch.Tensor | None:
     """Runs the step's tokens; returns float32 logits [R, vocab] at ctx.logit_rows."""
-    stream = ResidualStream(self.embedding.forward(ctx))
+    first = self.embedding.forward(ctx)
+    again = None
+    if any(call.add_embedding for call in self.spec.run_order):
+      # The stream is updated in place: what is added again later is a copy, in the activation
+      # dtype where that holds the embedding exactly (then it rides along with the pending branch).
+      exact = self.embedding.rides_exactly(ctx.ops.dtype) if hasattr(self.embedding, "rides_exactly") else False
+      again = ctx.ops.cast(first, ctx.ops.dtype) if exact else first
+      if again is first:
+        again = first.clone()
+    stream = ResidualStream(first)
+    layer_outputs = ctx.memo.get("layer_outputs")  # a list: the stream after every layer call (debugging, tests)
     for call, cache in zip(self.spec.run_order, self.cache_names):
+      if call.add_embedding:
+        stream.add_input(again, ctx)
       self.blocks[call.layer].forward(stream, ctx, caches.get(cache), call.writes_cache)
+      if layer_outputs is not None:
+        stream.flush(ctx)
+        layer_outputs.append(stream.h.clone())
     if ctx.logit_rows.numel() == 0:
       return None
     x = stream.normed(self.final_norm, ctx, rows=ctx.logit_rows)

@@ -34,8 +34,8 @@ class ReferenceOps:
   def linear(self, x, w):
     return (x.float() @ w.float().t()).to(self.dtype)
 
-  def gated_linear(self, x, w_gate_up, activation):
-    return self.gated_activation(self.linear(x, w_gate_up), activation)
+  def gated_linear(self, x, w_gate_up, activation, limit=0.0):
+    return self.gated_activation(self.linear(x, w_gate_up), activation, limit)
 
   def cast(self, x, dtype):
     return x.to(dtype)
@@ -55,9 +55,12 @@ class ReferenceOps:
       logits = cap * torch.tanh(logits / cap)
     return logits
 
-  def gated_activation(self, gate_up, activation):
+  def gated_activation(self, gate_up, activation, limit=0.0):
     f = gate_up.shape[1] // 2
     g, u = gate_up[:, :f].float(), gate_up[:, f:].float()
+    if activation == 3:
+      g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+      return (g * torch.sigmoid(1.702 * g) * (u + 1.0)).to(self.dtype)
     if activation == 0:
       a = 0.5 * g * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g + 0.044715 * g ** 3)))
     elif activation == 1:
@@ -277,6 +280,88 @@ class ReferenceOps:
     return out.reshape(t, num_heads * value_dim).to(self.dtype)
 
   # ---- gated delta rule -------------------------------------------------------
+
+  # ---- attention with heads normed one by one -----------------------------------
+  def rotate_headnorm_store(self, proj, eps, q_scale, rot_freq, *, interleaved, head_norm, tie_values, num_heads,
+                            num_kv_heads, head_dim, storage, block_table, ctx):
+    t = proj.shape[0]
+    nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+    q = proj[:, :nq].float().reshape(t, num_heads, head_dim)
+    k_raw = proj[:, nq:nq + nk].float().reshape(t, num_kv_heads, head_dim)
+    v = k_raw if tie_values else proj[:, nq + nk:nq + 2 * nk].float().reshape(t, num_kv_heads, head_dim)
+
+    def prepare(x):
+      x = x.clone()
+      if rot_freq is not None:
+        dims = 2 * rot_freq.numel()
+        angle = ctx.positions.float()[:, None, None] * rot_freq.float()[None, None, :]
+        c, s = torch.cos(angle), torch.sin(angle)
+        ia = torch.arange(0, dims, 2) if interleaved else torch.arange(0, dims // 2)
+        ib = ia + 1 if interleaved else ia + dims // 2
+        a, b = x[..., ia], x[..., ib]
+        x[..., ia], x[..., ib] = a * c - b * s, b * c + a * s
+      if head_norm:
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+      return x
+
+    if storage is not None:
+      ps = ctx.page_size
+      pos = ctx.positions.long()
+      page = block_table[ctx.token_seq.long(), pos // ps].long()
+      assert (page >= 0).all(), "a token would be written to a page the request does not hold"
+      storage[page, 0, :, pos % ps, :] = prepare(k_raw).to(storage.dtype)
+      storage[page, 1, :, pos % ps, :] = v.to(storage.dtype)
+    return (prepare(q) * q_scale).to(self.dtype)
+
+  def sigmoid_gate(self, x, proj, offset):
+    return (x.float() * torch.sigmoid(proj[:, offset:offset + x.shape[1]].float())).to(self.dtype)
+
+  # ---- forget-gate recurrence -----------------------------------------------------
+  def forget_gate_scan(self, pre, bias, lower, state, ctx, *, num_heads, head_dim, value_dim):
+    t = pre.shape[0]
+    n = num_heads * head_dim
+    pq = pre[:, :n].float()
+    q = (pq * torch.sigmoid(pq)).reshape(t, num_heads, head_dim)
+    f = (lower + (1.0 - lower) * torch.sigmoid(pre[:, n:2 * n].float() + bias)).reshape(t, num_heads, head_dim)
+    v = pre[:, 2 * n:2 * n + num_heads * value_dim].float().reshape(t, num_heads, value_dim)
+    out = torch.empty(t, num_heads, value_dim, dtype=torch.float32, device=pre.device)
+    for b in range(ctx.num_seqs):
+      r0, r1 = int(ctx.host["cu_q"][b]), int(ctx.host["cu_q"][b + 1])
+      slot = int(ctx.host["slots"][b])
+      s = state[slot].clone()
+      for r in range(r0, r1):
+        s = f[r][:, :, None] * s + (1.0 - f[r])[:, :, None] * v[r][:, None, :]
+        out[r] = torch.einsum("hdv,hd->hv", s, q[r])
+      state[slot] = s
+    return out
+
+  # ---- routed experts ---------------------------------------------------------------
+  def route_tokens(self, x, router, correction, shared_gate_w, *, top, scale, score=0, renormalize=False):
+    z = x.float() @ router.float().t()
+    s = torch.softmax(z, dim=-1) if score == 0 else torch.sigmoid(z)
+    choice = s + (correction.float() if correction is not None else 0.0)
+    chosen = torch.argsort(-choice, dim=-1, stable=True)[:, :top]
+    weight = torch.gather(s, 1, chosen)
+    weight = weight / weight.sum(-1, keepdim=True) * scale if renormalize else weight * scale
+    gate = torch.sigmoid(x.float() @ shared_gate_w.float()) if shared_gate_w is not None else None
+    return chosen.to(torch.int32), weight, gate
+
+  def mix_experts(self, x, chosen, weight, gate_up, down, num_experts, activation, shared, shared_gate):
+    xf = x.float()
+    out = torch.zeros_like(xf)
+    for t in range(x.shape[0]):
+      for j in range(chosen.shape[1]):
+        e = int(chosen[t, j])
+        if e < num_experts:
+          h = self.gated_activation((xf[t:t + 1] @ gate_up[e].float().t()).to(self.dtype), activation)
+          y = (h.float() @ down[e].float().t()).to(self.dtype).float()[0]
+        else:
+          y = xf[t]
+        out[t] += weight[t, j] * y
+    if shared is not None:
+      out += shared.float() * (shared_gate[:, None] if shared_gate is not None else 1.0)
+    return out.to(self.dtype)
+
   def delta_rule_inputs(self, pre, low, conv_weight, conv_state, decay_bias, neg_rate, ctx, *, conv_taps,
                         num_heads, num_kv_heads, head_dim, value_dim):
     t = pre.shape[0]
@@ -324,6 +409,8 @@ class ReferenceOps:
   def gated_head_norm(self, o, low, gate_offset, weight, eps, num_heads, value_dim):
     t = o.shape[0]
     y = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight.float()[None, None, :]
+    if low is None:
+      return y.reshape(t, num_heads * value_dim).to(self.dtype)
     gate = torch.sigmoid(low[:, gate_offset:gate_offset + num_heads * value_dim].float())
     return (y.reshape(t, num_heads * value_dim) * gate).to(self.dtype)
 
