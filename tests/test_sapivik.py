@@ -1,0 +1,280 @@
+"""The Sapivik decoder through the engine against the plain NumPy model.
+
+Each scenario runs on the CPU with the plain PyTorch kernel statements (this checks the parts,
+the configuration, the cache manager and the step function) and, marked `gpu`, with the CUDA
+kernels in float32 and bfloat16."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from simply_b200 import Engine, EngineConfig, SamplingParams, StepEntry
+from simply_b200.config import ConfigError, config_from_dict, load_config
+from simply_b200.weights import write_model_folder
+from tests import sapivik_cases as sx
+from tests.plain import sapivik_plain as plain
+from tests.reference_ops import ReferenceOps
+
+CPU = pytest.param(("float32", "cpu"), id="cpu")
+GPU32 = pytest.param(("float32", "cuda"), id="gpu-f32", marks=pytest.mark.gpu)
+GPU16 = pytest.param(("bfloat16", "cuda"), id="gpu-bf16", marks=pytest.mark.gpu)
+WHERE = [CPU, GPU32, GPU16]
+CONFIGS = {"a": sx.CONFIG_A, "b": sx.CONFIG_B, "c": sx.CONFIG_C}
+
+
+def engine_for(cfg_dict, where, seed=0, tensors=None, **kw):
+  dtype, device = where
+  cfg, t = sx.weights(cfg_dict, seed)
+  if tensors is not None:
+    t = tensors
+  ops = ReferenceOps(torch.float32) if device == "cpu" else None
+  return sx.build_engine(cfg, t, dtype, device, ops, **kw), t
+
+
+def tokens_for(cfg_dict, n, seed):
+  return np.random.default_rng(seed).integers(0, cfg_dict["vocab"], n).tolist()
+
+
+# ---- whole prompts, portions, decoding, batches -------------------------------------------------
+
+@pytest.mark.parametrize("where", WHERE)
+@pytest.mark.parametrize("which", ["a", "b", "c"])
+def test_whole_portions_and_decoding(which, where):
+  cfg_dict = CONFIGS[which]
+  engine, t = engine_for(cfg_dict, where, seed=3)
+  toks = tokens_for(cfg_dict, 61, 1)
+  want = plain.forward(cfg_dict, sx.as_numpy(t), toks)
+  n = len(toks)
+  for what, cuts in [
+      ("whole", [n]),
+      ("token by token", [1] * n),
+      ("prompt then decoding", [n - 40] + [1] * 40),
+      ("portions down to two tokens", sx.cuts_of(n, [7, 2, 5, 3, 11, 2, 13, 4, 2, 9])),
+      ("portions that end at the pages' borders", sx.cuts_of(n, [8, 8, 1, 7, 16, 2])),
+      ("portions of two", [2] * (n // 2) + [1]),
+      ("one token, then the rest", [1, n - 1]),
+  ]:
+    sx.check_close(sx.run_cuts(engine, toks, cuts), want, where[0], f"{which}: {what}")
+  engine.cache.check_invariants()
+  assert engine.cache.all_pages_free()
+  engine.ops.check_errors()
+
+
+@pytest.mark.parametrize("where", WHERE)
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_unequal_requests_side_by_side_with_pages_and_slots_used_again(which, where):
+  cfg_dict = CONFIGS[which]
+  # room for three live requests of these lengths, not for all six: pages and slots come back
+  engine, t = engine_for(cfg_dict, where, seed=5, slots=3, max_cache_tokens=3 * 80, poison=True)
+  lengths = [70, 9, 33, 1, 58, 21]
+  requests = [tokens_for(cfg_dict, n, 10 + i) for i, n in enumerate(lengths)]
+  w = sx.as_numpy(t)
+  want = [plain.forward(cfg_dict, w, r) for r in requests]
+  got = sx.run_mixed(engine, requests, seed=2)
+  for i, (g, x) in enumerate(zip(got, want)):
+    sx.check_close(g, x, where[0], f"request {i} in a mixed batch")
+  # the same requests once more through the used slots and pages, each alone
+  for i in (0, 4):
+    sx.check_close(sx.run_cuts(engine, requests[i], [len(requests[i])]), want[i], where[0], f"request {i} again")
+  engine.cache.check_invariants()
+  assert engine.cache.all_pages_free()
+  engine.ops.check_errors()
+
+
+@pytest.mark.parametrize("where", WHERE)
+def test_long_decoding_past_many_pages(where):
+  cfg_dict = sx.CONFIG_A
+  engine, t = engine_for(cfg_dict, where, seed=7, page_size=4)
+  toks = tokens_for(cfg_dict, 150, 4)
+  want = plain.forward(cfg_dict, sx.as_numpy(t), toks)
+  sx.check_close(sx.run_cuts(engine, toks, [3] + [1] * 147), want, where[0], "long decoding")
+  engine.ops.check_errors()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_pages_of_64_and_head_sizes_of_the_tensor_core_kernels(dtype):
+  """600 tokens over pages of 64: head sizes 64 and 128 with four and two heads per kv head (the
+  tensor-core attention kernels in bfloat16), recurrent heads wider than a warp's rows, more
+  routed rows per expert than one tile holds."""
+  cfg_dict = sx.config(
+      [sx.attention(heads=8, kv_heads=2, dim=64, dims=32, base=5000.0, scale=0.1, softcap=20.0),
+       sx.hgrn2(heads=2, dim=64, vdim=128), sx.attention(heads=4, kv_heads=2, dim=128, dims=64, scale=0.07),
+       sx.hgrn2(heads=4, dim=128, vdim=32)],
+      [sx.moe(experts=3, identity=1, top=2, ff=96, shared=128), sx.dense(ff=256, limit=2.5), sx.moe(experts=8, identity=0, top=4, ff=32, shared=0), None],
+      width=128, vocab=300, loop=(1, 3, 2))
+  cfg, t = sx.weights(cfg_dict, seed=3, matrix_std=0.1)
+  engine = sx.build_engine(cfg, t, dtype, "cuda", None, page_size=64, slots=2, max_seq_len=1024)
+  toks = tokens_for(cfg_dict, 600, 1)
+  want = plain.forward(cfg_dict, sx.as_numpy(t), toks)
+  for what, cuts in [("whole", [600]), ("portions", sx.cuts_of(600, [100, 2, 37, 64, 3, 129, 200])),
+                     ("decoding", [540] + [1] * 60)]:
+    sx.check_close(sx.run_cuts(engine, toks, cuts), want, dtype, what)
+  engine.ops.check_errors()
+
+
+# ---- a key that stands out, a state that remembers --------------------------------------------------
+
+@pytest.mark.parametrize("where", WHERE)
+def test_a_key_far_back_that_stands_out(where):
+  """One attention layer whose query of token 1 is answered by the key of token 2 alone, however far
+  back and wherever in a page it lies; the needle among hundreds of other keys."""
+  cfg_dict = sx.config([sx.attention(heads=4, kv_heads=2, dim=16, dims=8, scale=1.0, softcap=30.0)], [sx.dense(ff=32)],
+                       width=32, vocab=50)
+  cfg, t = sx.weights(cfg_dict, seed=11)
+  sx.plant_needle(cfg_dict, t, 0, needle=2, asker=1)
+  w = sx.as_numpy(t)
+  engine, _ = engine_for(cfg_dict, where, tensors=t, page_size=8, max_seq_len=512)
+  rng = np.random.default_rng(0)
+  seen_change = False
+  for n, needle_at, ask_at in [(40, 0, 1), (40, 0, 39), (75, 7, 8), (75, 8, 71), (75, 3, 16), (330, 1, 329), (330, 15, 200)]:
+    toks = rng.integers(3, cfg_dict["vocab"], n).tolist()
+    toks[needle_at], toks[ask_at] = 2, 1
+    want = plain.forward(cfg_dict, w, toks)
+    without = list(toks)
+    without[needle_at] = 5
+    if np.abs(plain.forward(cfg_dict, w, without)[ask_at] - want[ask_at]).max() > 0.5:
+      seen_change = True  # the needle decides the asker's logits here
+    for cuts in ([n], [ask_at, 1, n], [max(ask_at - 1, 1), 2, n], sx.cuts_of(n, [5, 2, 3, 64]), [needle_at + 1, ask_at - needle_at - 1] + [1] * 8 + [n]):
+      got = sx.run_cuts(engine, toks, [c for c in cuts if c > 0])
+      sx.check_close(got, want, where[0], f"needle at {needle_at}, asked at {ask_at}, cuts {cuts[:3]}")
+  assert seen_change, "the planted key never decided anything: the test's weights are too weak"
+  engine.ops.check_errors()
+
+
+@pytest.mark.parametrize("where", WHERE)
+def test_state_that_remembers_far_back(where):
+  """Only the recurrence's state connects the last token with the first ones, so a state that is
+  lost, zeroed or mixed up between slots shows."""
+  cfg_dict = sx.config([sx.hgrn2(heads=2, dim=16, vdim=16)], [sx.dense(ff=32)], width=32, vocab=60)
+  engine, t = engine_for(cfg_dict, where, seed=21)
+  w = sx.as_numpy(t)
+  a, b = tokens_for(cfg_dict, 48, 1), tokens_for(cfg_dict, 48, 2)
+  c = list(a)
+  c[2] = (c[2] + 1) % cfg_dict["vocab"]
+  want_a, want_c = plain.forward(cfg_dict, w, a), plain.forward(cfg_dict, w, c)
+  assert np.abs(want_a[-1] - want_c[-1]).max() > 5e-3 * np.abs(want_a).max(), "the state forgets too fast for this test"
+  got = sx.run_mixed(engine, [a, b, c], seed=5, max_live=3, portions=(2, 3, 4))
+  sx.check_close(got[0], want_a, where[0], "a")
+  sx.check_close(got[1], plain.forward(cfg_dict, w, b), where[0], "b")
+  sx.check_close(got[2], want_c, where[0], "c")
+
+
+# ---- generation through the entry point and the scheduler -----------------------------------------
+
+@pytest.mark.parametrize("where", [CPU, GPU32])
+def test_greedy_generation_through_the_scheduler(where):
+  cfg_dict = sx.CONFIG_B
+  engine, t = engine_for(cfg_dict, where, seed=9, slots=2)
+  w = sx.as_numpy(t)
+  prompts = [tokens_for(cfg_dict, n, 30 + i) for i, n in enumerate((5, 17, 1, 26))]
+  results = engine.generate(prompts, SamplingParams(temperature=0.0, max_decode_steps=12))
+  for prompt, r in zip(prompts, results):
+    toks = list(prompt)
+    for _ in range(12):
+      toks.append(int(np.argmax(plain.forward(cfg_dict, w, toks)[-1])))
+    assert r.output_token_ids == toks[len(prompt):], (r.output_token_ids, toks[len(prompt):])
+  assert engine.cache.all_pages_free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("which,burst", [("a", 1), ("b", 5)])
+def test_decoding_from_cuda_graphs(which, burst):
+  """Three live requests decode from the graph of four rows (the fourth repeats the third and
+  must not touch its state a second time), several steps per replay burst."""
+  cfg_dict = CONFIGS[which]
+  engine, t = engine_for(cfg_dict, ("float32", "cuda"), seed=13, slots=4, graphs=True, burst=burst)
+  assert engine._decode_runner is not None, "the model's parts must all allow graph capture"
+  w = sx.as_numpy(t)
+  prompts = [tokens_for(cfg_dict, n, 40 + i) for i, n in enumerate((9, 3, 14))]
+  results = engine.generate(prompts, SamplingParams(temperature=0.0, max_decode_steps=17))
+  assert engine._decode_runner.bursts > 0
+  for prompt, r in zip(prompts, results):
+    toks = list(prompt)
+    for _ in range(17):
+      toks.append(int(np.argmax(plain.forward(cfg_dict, w, toks)[-1])))
+    assert r.output_token_ids == toks[len(prompt):], (r.output_token_ids, toks[len(prompt):])
+  engine.ops.check_errors()
+
+
+@pytest.mark.gpu
+def test_bfloat16_generation_runs_and_samples():
+  engine, _ = engine_for(sx.CONFIG_A, ("bfloat16", "cuda"), seed=2, slots=3)
+  prompts = [tokens_for(sx.CONFIG_A, n, i) for i, n in enumerate((4, 30, 11, 2, 19))]
+  results = engine.generate(prompts, SamplingParams(temperature=0.8, top_k=20, max_decode_steps=20, seed=4))
+  assert all(len(r.output_token_ids) == 20 for r in results)
+  again = engine.generate(prompts, SamplingParams(temperature=0.8, top_k=20, max_decode_steps=20, seed=4))
+  assert [r.output_token_ids for r in results][0] == [r.output_token_ids for r in again][0]
+  engine.ops.check_errors()
+
+
+@pytest.mark.gpu
+def test_bfloat16_single_tokens_replayed_from_cuda_graphs():
+  cfg_dict = sx.CONFIG_A
+  engine, t = engine_for(cfg_dict, ("bfloat16", "cuda"), seed=6, slots=4, graphs=True)
+  assert engine._decode_runner is not None
+  engine._decode_runner.keep_logits = True
+  w = sx.as_numpy(t)
+  requests = [tokens_for(cfg_dict, n, 50 + i) for i, n in enumerate((70, 41, 55))]
+  want = [plain.forward(cfg_dict, w, r) for r in requests]
+  slots = [engine.open_request() for _ in requests]
+  heads = [len(r) - 30 for r in requests]
+  engine.step_raw([StepEntry(s, r[:h], ()) for s, r, h in zip(slots, requests, heads)])
+  got = [[] for _ in requests]
+  for step in range(30):
+    entries = [StepEntry(s, [r[h + step]], (0,)) for s, r, h in zip(slots, requests, heads)]
+    logits = engine.step_raw(entries, from_graph=True).float().cpu().numpy()
+    for i in range(len(requests)):
+      got[i].append(logits[i])
+  for i, h in enumerate(heads):
+    sx.check_close(np.stack(got[i]), want[i][h:], "bfloat16", f"request {i}, replayed steps")
+  engine.ops.check_errors()
+
+
+# ---- configuration, model folders, the command line ---------------------------------------------------
+
+def test_config_round_trip_run_order_and_errors():
+  cfg = config_from_dict(sx.CONFIG_A)
+  assert config_from_dict(cfg.to_dict()) == cfg
+  spec = cfg.model_spec()
+  order = [(c.layer, c.add_embedding) for c in spec.run_order]
+  assert order == [("l0", False), ("l1", False), ("l2", False), ("l0", True), ("l1", False), ("l2", False), ("l3", False)]
+  assert len(set(spec.cache_names())) == 7  # every pass has a memory of its own
+  assert [c.layer for c in config_from_dict(sx.CONFIG_B).model_spec().run_order] == ["l0", "l1", "l1", "l1", "l2", "l3"]
+  assert [c.layer for c in config_from_dict(sx.CONFIG_C).model_spec().run_order] == ["l0", "l1"]
+  assert plain.run_order(sx.CONFIG_B) == [(0, False), (1, False), (1, True), (1, True), (2, False), (3, False)]
+  for change, text in [
+      (lambda d: d["layers"][0].update(type="conv"), "unknown type"),
+      (lambda d: d["layers"][0]["mixer"].update(vdim=8), "vdim must equal dim"),
+      (lambda d: d["layers"][0]["mixer"]["rot"].update(dims=5), "rot.dims"),
+      (lambda d: d["layers"][1]["mlp"]["router"].update(top=9), "router must choose"),
+      (lambda d: d.update(loop={"start": 2, "stop": 1, "times": 2}), "loop"),
+      (lambda d: d["layers"][0]["mlp"].update(kind="sparse"), "unknown mlp kind"),
+  ]:
+    import copy
+    d = copy.deepcopy(sx.CONFIG_A)
+    change(d)
+    with pytest.raises(ConfigError, match=text):
+      config_from_dict(d)
+
+
+def test_model_folder_and_the_step_function_on_it(tmp_path):
+  cfg = config_from_dict(sx.CONFIG_B)
+  folder = write_model_folder(cfg, 4, str(tmp_path / "m"), matrix_std=0.2, scale_std=0.1)
+  assert load_config(folder) == cfg
+  with open(os.path.join(folder, "config.json")) as f:
+    assert json.load(f)["architecture"] == "Sapivik"
+  ec = EngineConfig(activation_dtype="float32", page_size=8, batch_size=2, max_seq_len=64, use_cuda_graphs=False)
+  engine = Engine.from_folder(folder, ec, ops=ReferenceOps(torch.float32), device="cpu")
+  from simply_b200.weights import safetensors_io as st
+  entries = st.index_files(st.model_files(folder))
+  reader = st.TensorReader(entries)
+  w = {n: reader.read(n).float().numpy() for n in entries}
+  toks = tokens_for(sx.CONFIG_B, 19, 3)
+  slot = engine.open_request()
+  got = engine.step_raw([StepEntry(slot, toks, tuple(range(len(toks))))]).numpy()
+  engine.close_request(slot)
+  sx.check_close(got, plain.forward(sx.CONFIG_B, w, toks), "float32", "a written folder")
