@@ -432,8 +432,8 @@ def profile_step(engine, torch, cfg, args, context):
 
 
 def design_arm(args):
-  """`--design generax`: see simply_b200/design_bench.py.  One JSON line; `value` is the design's
-  decode throughput at the first size."""
+  """`--design generax|sapivik`: see simply_b200/design_bench.py.  One JSON line; `value` is the
+  design's decode throughput at the first size."""
   import torch
 
   from simply_b200 import design_bench
@@ -442,17 +442,18 @@ def design_arm(args):
   peaks, peaks_from = load_peaks()
   sampler = ClockSampler()
   sampler.start()
-  res = design_bench.run(args, peaks, time_decode)
+  res = design_bench.run(args, peaks, time_decode, args.design)
+  name, other = design_bench.PAIRS[args.design]
   clocks = sampler.stop()
   first = next(iter(res["sizes"].values()))
   print(json.dumps({
-      "metric": "decode tok/s @ batch 8, 2048-token context (Generax at the first size, 1 B200); prefill and "
-                "Gemma 2 at equal size in `sizes`",
-      "value": first["generax"]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-      "warmup": args.warmup, "ms_per_step": first["generax"]["decode_ms_per_step"], "higher_is_better": True,
+      "metric": f"decode tok/s @ batch 8, 2048-token context ({name} at the first size, 1 B200); prefill and "
+                f"{other} at equal size in `sizes`",
+      "value": first[name]["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+      "warmup": args.warmup, "ms_per_step": first[name]["decode_ms_per_step"], "higher_is_better": True,
       "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
       "data": "synthetic: random bf16 weights N(0, 0.02) seed 0, uniform random token ids", "impl": "ours",
-      "config": {"model": "generax beside gemma2", "global_batch": 8, "seq_len": 2048, "parallelism": "1 GPU",
+      "config": {"model": f"{name} beside {other}", "global_batch": 8, "seq_len": 2048, "parallelism": "1 GPU",
                  "l2": "whole steps: inputs larger than L2; single calls: L2 flushed before each", "peaks": peaks_from},
       "gpu_launches": res["launches"], "sizes": res["sizes"], "clocks": clocks}))
   return 0
@@ -473,9 +474,9 @@ def main(argv=None):
   ap.add_argument("--profile", choices=["decode", "prefill", "mixed"], default=None,
                   help="run ONE eager step of this kind between cudaProfilerStart/Stop and exit "
                        "(for ncu --profile-from-start off); prints no benchmark line")
-  ap.add_argument("--design", choices=["generax"], default=None,
+  ap.add_argument("--design", choices=["generax", "sapivik"], default=None,
                   help="instead of the default workload: prefill and decode throughput of this design beside "
-                       "Gemma 2 at equal size (layer shapes like a real model's, random weights), and every "
+                       "the engine's closest other model (Gemma 2 for generax, generax for sapivik) at equal size (layer shapes like a real model's, random weights), and every "
                        "kernel call of one step of each timed alone against the measured peaks")
   args = ap.parse_args(argv)
   if args.impl == "reference":

@@ -7,7 +7,7 @@
 // Local row r of the tile is weight row base0 + r for r < 64 and base0 + second + (r - 64)
 // beyond.  Epilogues: 0 bfloat16; 1 float32 with soft cap (simply/model_lib.py:107-109, the
 // output layer); 2 gated activation: rows r < 64 are gate rows, r + 64 their up rows
-// (simply/model_lib.py:722-726); 3 the fused q, k, v projection: rows r < 64 are 64 dims of a
+// (simply/model_lib.py:722-726; the clamped activation reads its limit from `cap`); 3 the fused q, k, v projection: rows r < 64 are 64 dims of a
 // head, r + 64 the dims half a head further; rotation (simply/utils/position_encoding.py:83-110),
 // query scale (simply/model_lib.py:2014-2019), keys and values into the pages of the cache.
 #pragma once
@@ -59,6 +59,17 @@ __device__ __forceinline__ float gated_act(float g, int act) {
   }
   if (act == 1) return g / (1.0f + expf(-g));
   return fmaxf(g, 0.f);
+}
+
+// act(gate) * up; activation 3 is the clamped form, which acts on both halves:
+// g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1).
+__device__ __forceinline__ float gated_pair(float g, float u, int act, float limit) {
+  if (act == 3) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return gated_act(g, act) * u;
 }
 
 // All threads of the block (and of every block of the cluster) call this once the block's tile
@@ -113,7 +124,7 @@ __device__ __forceinline__ void finish_tile(float* sums, int tokens, int M, int 
           // Round gate and up to bfloat16 first, as the unfused path stores them.
           const float gate = __bfloat162float(__float2bfloat16_rn(total(token, r)));
           const float up = __bfloat162float(__float2bfloat16_rn(total(token, 64 + r)));
-          reinterpret_cast<bf16*>(out)[(size_t)token * tg.rows_end + n] = __float2bfloat16_rn(gated_act(gate, act) * up);
+          reinterpret_cast<bf16*>(out)[(size_t)token * tg.rows_end + n] = __float2bfloat16_rn(gated_pair(gate, up, act, cap));
         }
       }
     } else {

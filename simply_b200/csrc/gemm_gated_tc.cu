@@ -85,12 +85,16 @@ __device__ __forceinline__ float gate_act(float g, int act) {
   return sbg::gated_act(g, act);
 }
 
+__device__ __forceinline__ float gate_pair(float g, float u, int act, float limit) {
+  return act == 3 ? sbg::gated_pair(g, u, act, limit) : gate_act(g, act) * u;
+}
+
 // A warp's part of a tile: 32 tokens (this warp's lanes of tensor memory) x 64 features from
 // feature c0 of the tile.  Gate and up sums from the accumulator at `acc`, the activation,
 // bfloat16 results to the warp's own 4 KB of shared memory (`stage`: 32 rows of 128 bytes, 16-byte
 // pieces swizzled as the TMA expects), then one TMA store to out[row0.., f0 + c0..].
 __device__ __forceinline__ void store_gated_rows(uint32_t acc, int c0, unsigned char* stage, const CUtensorMap* map_out,
-                                                 int row0, int f0, int act) {
+                                                 int row0, int f0, int act, float limit) {
   const int lane = threadIdx.x & 31;
   if (lane == 0) tma_store_wait_read();  // the store of the tile before has read the stage
   __syncwarp();
@@ -109,7 +113,7 @@ __device__ __forceinline__ void store_gated_rows(uint32_t acc, int c0, unsigned 
       const uint32_t up = pack_bf16(__uint_as_float(u[i]), __uint_as_float(u[i + 1]));
       const float g0 = __uint_as_float(gp << 16), g1 = __uint_as_float(gp & 0xFFFF0000u);
       const float u0 = __uint_as_float(up << 16), u1 = __uint_as_float(up & 0xFFFF0000u);
-      packed[i / 2] = pack_bf16(gate_act(g0, act) * u0, gate_act(g1, act) * u1);
+      packed[i / 2] = pack_bf16(gate_pair(g0, u0, act, limit), gate_pair(g1, u1, act, limit));
     }
     unsigned char* srow = stage + lane * 128;
     const int piece = c / 8;  // 16-byte pieces of the row: two per 16 features
@@ -126,7 +130,7 @@ __device__ __forceinline__ void store_gated_rows(uint32_t acc, int c0, unsigned 
 
 __global__ void __launch_bounds__(THREADS, 1)
 gated_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                const __grid_constant__ CUtensorMap map_out, int M, int F, int K, int act, int* err) {
+                const __grid_constant__ CUtensorMap map_out, int M, int F, int K, int act, float limit, int* err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
@@ -242,7 +246,7 @@ gated_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         break;
       }
       tc_fence_after_sync();
-      store_gated_rows(tmem + lane_base + buf * ACC_COLS, c0, out_stage, &map_out, m0 + quarter * 32, f0, act);
+      store_gated_rows(tmem + lane_base + buf * ACC_COLS, c0, out_stage, &map_out, m0 + quarter * 32, f0, act, limit);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -270,7 +274,7 @@ constexpr size_t PAIR_SMEM_BYTES = (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + OUT_
 
 __global__ void __launch_bounds__(THREADS, 1)
 gated_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                     const __grid_constant__ CUtensorMap map_out, int M, int F, int K, int act, int* err) {
+                     const __grid_constant__ CUtensorMap map_out, int M, int F, int K, int act, float limit, int* err) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* tiles = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t full[PAIR_STAGES], empty[PAIR_STAGES], acc_full[2], acc_empty[2];
@@ -379,7 +383,7 @@ gated_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         break;
       }
       tc_fence_after_sync();
-      store_gated_rows(tmem + lane_base + buf * ACC_COLS, c0, out_stage, &map_out, m0 + quarter * 32, f0, act);
+      store_gated_rows(tmem + lane_base + buf * ACC_COLS, c0, out_stage, &map_out, m0 + quarter * 32, f0, act, limit);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[buf]), 0));
@@ -428,10 +432,10 @@ int weight_map(CUtensorMap* map, const void* w, long long rows, long long cols) 
 // does not take (the caller then uses another product): F not a multiple of 128, K not a
 // multiple of 8, operands not 16-byte aligned.  blocks: 0 = one per SM.  pairs: 1 = blocks work in
 // pairs on tiles of 256 tokens, 0 = each alone on tiles of 128.
-extern "C" int sb_gemm_gated_tc(const void* x, const void* w, void* out, int M, int F, int K, int act, int blocks,
-                                int pairs, int* err, cudaStream_t stream) {
+extern "C" int sb_gemm_gated_tc(const void* x, const void* w, void* out, int M, int F, int K, int act, float limit,
+                                int blocks, int pairs, int* err, cudaStream_t stream) {
   if (M == 0 || F == 0) return 0;
-  if (F % BF != 0 || K % 8 != 0 || K <= 0 || act < 0 || act > 2) return -9;
+  if (F % BF != 0 || K % 8 != 0 || K <= 0 || act < 0 || act > 3) return -9;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) return -9;
   static int configured = -1, num_sms = 0, max_pairs = 0;
   if (configured < 0) {
@@ -488,7 +492,7 @@ extern "C" int sb_gemm_gated_tc(const void* x, const void* w, void* out, int M, 
     ++n_attr;
     config.attrs = attribute;
     config.numAttrs = n_attr;
-    cudaError_t e = cudaLaunchKernelEx(&config, gated_tc_pair_kernel, map_x, map_w, map_out, M, F, K, act, err);
+    cudaError_t e = cudaLaunchKernelEx(&config, gated_tc_pair_kernel, map_x, map_w, map_out, M, F, K, act, limit, err);
     if (e != cudaSuccess) return (int)e;
     SB_LAUNCH_CHECK();
     return 0;
@@ -496,7 +500,7 @@ extern "C" int sb_gemm_gated_tc(const void* x, const void* w, void* out, int M, 
   const int num_tiles = ((M + BM - 1) / BM) * (F / BF);
   const int grid = min(num_tiles, blocks > 0 ? blocks : num_sms);
   cudaError_t e = sb_launch_early(gated_tc_kernel, dim3(grid), dim3(THREADS), SMEM_BYTES, stream, map_x, map_w,
-                                  map_out, M, F, K, act, err);
+                                  map_out, M, F, K, act, limit, err);
   if (e != cudaSuccess) return (int)e;
   SB_LAUNCH_CHECK();
   return 0;

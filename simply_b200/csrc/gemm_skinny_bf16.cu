@@ -46,6 +46,16 @@ __device__ __forceinline__ float skinny_activation(float g, int act) {
   return fmaxf(g, 0.f);
 }
 
+// act(gate) * up; activation 3 (clamped) acts on both halves and reads its limit from `cap`.
+__device__ __forceinline__ float skinny_gated_pair(float g, float u, int act, float limit) {
+  if (act == 3) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return skinny_activation(g, act) * u;
+}
+
 __device__ __forceinline__ void mma_bf16_16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -216,7 +226,7 @@ skinny_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, void*
       // Round gate and up to bfloat16 first, as the unfused path stores them.
       const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
       const float up = __bfloat162float(__float2bfloat16_rn(v[SETS - 1]));
-      reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(skinny_activation(gate, act) * up);
+      reinterpret_cast<bf16*>(out)[o] = __float2bfloat16_rn(skinny_gated_pair(gate, up, act, cap));
     }
   }
 }
@@ -265,7 +275,7 @@ extern "C" int sb_gemm_skinny_bf16(const void* x, const void* w, void* out, int 
                                    float cap, int act, int warps_override, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (M > 32 || K % 8 != 0 || K <= 0 || epilogue < 0 || epilogue > 2) return -9;
-  if (epilogue == 2 && (N % 2 != 0 || act < 0 || act > 2)) return -9;
+  if (epilogue == 2 && (N % 2 != 0 || act < 0 || act > 3)) return -9;
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)w;
   const int n_out = epilogue == 2 ? N / 2 : N;

@@ -333,7 +333,7 @@ extern "C" int sb_gemm_stream_tc(const void* x, const void* w, void* out, int M,
                                  int act, int split_override, int stages, int* err, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   if (M > 128 || K % 8 != 0 || K <= 0 || epilogue < 0 || epilogue > 2) return -9;
-  if (epilogue == 2 && (N % 2 != 0 || act < 0 || act > 2)) return -9;
+  if (epilogue == 2 && (N % 2 != 0 || act < 0 || act > 3)) return -9;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -9;
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)w;

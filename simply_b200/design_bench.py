@@ -1,7 +1,8 @@
-"""Prefill and decode throughput of the Generax design beside Gemma 2 at equal size, and the time
-of every kernel call of one step of each with its share of the measured peaks.
+"""Prefill and decode throughput of a design beside the engine's closest other model at equal size
+(Generax beside Gemma 2, Sapivik beside Generax), and the time of every kernel call of one step of
+each with its share of the measured peaks.
 
-Used by `bench.py --design generax` (the default benchmark does not import this file).  Layer
+Used by `bench.py --design generax|sapivik` (the default benchmark does not import this file).  Layer
 shapes resemble a real model's; weights are random.  Per size and design:
 
 * prefill: one 2,048-token prompt in one step, median of 5 after 3 warm-up steps, CUDA events;
@@ -48,6 +49,30 @@ def generax_dict(s: dict) -> dict:
     layers[-1]["mlp"] = {"kind": "dense", "ff": s["ff"]}
   return {"architecture": "Generax", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
           "logit_softcap": 30.0, "layers": layers, "max_context": 8192}
+
+
+def sapivik_dict(s: dict) -> dict:
+  """Attention layers with a dense feed-forward and recurrent layers with routed experts in turn (one
+  in three is attention, as one in three Generax layers has keys of its own); the experts' hidden
+  size is a quarter of the dense one, four of sixteen chosen, so a token's products are those of a
+  dense layer; the first three layers run twice."""
+  att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+         "scale": s["dim"] ** -0.5, "softcap": 30.0, "rot": {"dims": s["dim"] // 2, "base": 10000.0}}
+  rec = {"heads": s["heads"], "dim": s["dim"], "vdim": s["dim"]}
+  dense = {"kind": "dense", "ff": s["ff"], "limit": 7.0}
+  experts = {"kind": "moe", "expert": {"ff": s["ff"] // 4}, "shared": {"ff": s["ff"] // 4},
+             "router": {"experts": 16, "identity": 2, "top": 4, "scale": 1.0}}
+  layers = []
+  for i in range(s["layers"]):
+    if i % 3 == 0:
+      layers.append({"type": "attention", "mixer": dict(att), "mlp": dict(dense)})
+    else:
+      layers.append({"type": "hgrn2", "mixer": dict(rec), "mlp": dict(experts)})
+  times = 2
+  stop = min(3, s["layers"])
+  return {"architecture": "Sapivik", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+          "residual_mult": 0.5, "layers": layers[:s["layers"] - stop * (times - 1)] if s["layers"] > stop else layers,
+          "loop": {"start": 0, "stop": stop, "times": times if s["layers"] > stop else 1}, "max_context": 8192}
 
 
 def gemma2_dict(s: dict) -> dict:
@@ -99,8 +124,12 @@ class TimedOps:
       if name in ("linear", "gated_linear", "lm_head"):
         x, w = args[0], args[1]
         flops = 2.0 * x.shape[0] * w.shape[0] * w.shape[1]
+      if name == "mix_experts":
+        t_, top_ = args[1].shape
+        if args[3] is not None:
+          flops = 2.0 * t_ * top_ * (args[3].shape[1] + args[4].shape[1]) * args[3].shape[2]
       if name in ("paged_attention", "project_rotate_store", "rope_and_cache_write", "qk_norm_rotate_store", "pool_blocks",
-                  "delta_rule_inputs", "gated_delta_scan"):
+                  "delta_rule_inputs", "gated_delta_scan", "rotate_headnorm_store", "forget_gate_scan"):
         moved -= big if name != "delta_rule_inputs" else 0  # the cache (or state) storage is not read whole
       if name == "paged_attention" and ctx is not None:
         q = args[0]
@@ -123,6 +152,9 @@ class TimedOps:
         per_slot = state[0].numel() * 4
         moved += 2 * per_slot * ctx.num_seqs  # the state is read and written once per sequence
         flops = 6.0 * args[0].shape[0] * kw["num_heads"] * kw["head_dim"] * kw["value_dim"]
+      if name == "forget_gate_scan" and ctx is not None:
+        moved += 2 * args[3][0].numel() * 4 * ctx.num_seqs
+        flops = 5.0 * args[0].shape[0] * kw["num_heads"] * kw["head_dim"] * kw["value_dim"]
       self.rows.append((name, out.shape[0] if isinstance(out, torch.Tensor) else 0, e0.elapsed_time(e1), moved, flops))
       return out
 
@@ -177,8 +209,12 @@ def _prefill_ms(engine, tokens: int, vocab: int) -> float:
   return float(np.median(times))
 
 
-def run(args, peaks: dict, time_decode) -> dict:
-  """Both designs at every size; `time_decode` is bench.py's burst timer."""
+PAIRS = {"generax": ("generax", "gemma2"), "sapivik": ("sapivik", "generax")}
+DICTS = {"generax": generax_dict, "gemma2": gemma2_dict, "sapivik": sapivik_dict}
+
+
+def run(args, peaks: dict, time_decode, design: str = "generax") -> dict:
+  """The design and its neighbour at every size; `time_decode` is bench.py's burst timer."""
   from simply_b200 import Engine, EngineConfig, StepEntry
   from simply_b200.config import config_from_dict
 
@@ -187,7 +223,7 @@ def run(args, peaks: dict, time_decode) -> dict:
   launches = 0
   for size_name, s in SIZES.items():
     results[size_name] = {"shape": s}
-    for design, d in (("generax", generax_dict(s)), ("gemma2", gemma2_dict(s))):
+    for design, d in ((name, DICTS[name](s)) for name in PAIRS[design]):
       cfg = config_from_dict(d)
       ec = EngineConfig(activation_dtype="bfloat16", page_size=64, batch_size=batch, max_seq_len=context + 64,
                         max_cache_tokens=batch * (context + 64), max_num_issue_tokens=2048, intermediate_steps=1)

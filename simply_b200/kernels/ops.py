@@ -233,7 +233,7 @@ class CudaOps:
         "sb_gemm_skinny_bf16": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void],
         "sb_gemm_stream_tc": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                               c_void, c_void],
-        "sb_gemm_gated_tc": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_int, c_void, c_void],
+        "sb_gemm_gated_tc": [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void, c_void],
         "sb_qkv_rope_stream_tc": [c_void, c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int,
                                   c_void, c_void, c_int, c_int, c_int, c_int, c_int, c_void, c_int, c_int, c_void],
         "sb_qkv_rope_skinny": [c_void, c_void, c_int, c_int, c_void, c_void, c_float, c_void, c_void, c_void, c_int,
@@ -631,25 +631,23 @@ class CudaOps:
     (clamped) takes `limit` and acts on both halves (csrc/elementwise.cu)."""
     m, k = x.shape
     n = w_gate_up.shape[0]
-    if activation == 3:
-      return self.gated_activation(self.linear(x, w_gate_up), activation, limit)
     if w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and m <= self.skinny_max_rows:
       out = self._new(m, n // 2, dtype=torch.bfloat16)
-      if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n, k, 2, 0.0,
+      if self._call("sb_gemm_skinny_bf16", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n, k, 2, float(limit),
                     activation, self.skinny_warps) == 0:
         return out
     if (w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and self.mid_rows_kernel
         and self.skinny_max_rows < m <= self.mid_rows["gated"] and x.is_contiguous() and w_gate_up.is_contiguous()):
       out = self._new(m, n // 2, dtype=torch.bfloat16)
-      if self._mid_product(x, w_gate_up, out, 2, activation=activation):
+      if self._mid_product(x, w_gate_up, out, 2, cap=limit, activation=activation):
         return out
     if (w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and m >= self.gated_tc_min_rows > 0
         and x.is_contiguous() and w_gate_up.is_contiguous()):
       out = self._new(m, n // 2, dtype=torch.bfloat16)
-      if self._call("sb_gemm_gated_tc", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n // 2, k, activation,
+      if self._call("sb_gemm_gated_tc", _ptr(x), _ptr(w_gate_up), _ptr(out), m, n // 2, k, activation, float(limit),
                     self.gated_tc_blocks, int(self.gated_tc_pairs), _ptr(self.err)) == 0:
         return out
-    return self.gated_activation(self.linear(x, w_gate_up), activation)
+    return self.gated_activation(self.linear(x, w_gate_up), activation, limit)
 
   def lm_head(self, x: torch.Tensor, table: torch.Tensor, cap: float) -> torch.Tensor:
     """float32 logits [R, vocab] = softcap(x . table^T)."""

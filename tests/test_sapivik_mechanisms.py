@@ -253,3 +253,22 @@ def test_one_layer_models(case, where):
   for i, (g, x) in enumerate(zip(outs, trace)):
     close(g.float().cpu().numpy(), x, torch.float32 if dtype == "float32" else torch.bfloat16, f"{case}: stream after call {i}",
           f32=3e-5, bf16=5e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows", [1, 8, 20, 40, 130, 300])
+@pytest.mark.parametrize("hidden,width", [(128, 64), (256, 320), (40, 24)])
+def test_the_clamped_gated_product_at_every_batch_size(rows, hidden, width, dtype):
+  """The product with the clamped activation on its sums: every kernel that serves some number of
+  rows (a handful, a serving batch, a prompt) against the plain statement."""
+  ops, dt = table((dtype, "cuda"))
+  rng = np.random.default_rng(rows + hidden)
+  x, x64 = held(rng.standard_normal((rows, width)), dt, "cuda")
+  w, w64 = held(rng.standard_normal((2 * hidden, width)) * 0.5, dt, "cuda")
+  got = ops.gated_linear(x, w, 3, limit=1.1).float().cpu().numpy()
+  gu = x64 @ w64.T
+  if dt == torch.bfloat16:  # the projections are held in the storage type before the activation
+    gu = torch.from_numpy(gu).to(torch.bfloat16).double().numpy()
+  g, u = np.minimum(gu[:, :hidden], 1.1), np.clip(gu[:, hidden:], -1.1, 1.1)
+  close(got, g * plain.sigmoid(1.702 * g) * (u + 1.0), dt, f"{rows} rows")
