@@ -24,14 +24,14 @@
 // route: one block per token.
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ x, int width, const float* __restrict__ router_w,
                  const float* __restrict__ correction, const float* __restrict__ shared_gate_w, int NE, int top,
                  float scale, int score_fn, int renormalize, int* __restrict__ chosen, float* __restrict__ weight,
                  float* __restrict__ shared_gate) {
   pdl_wait_block();
   pdl_launch_dependents();
-  extern __shared__ float route_smem[];  // x [width], z [NE + 1], choice [NE]
+  extern __shared__ __align__(16) float route_smem[];  // x [width], z [NE + 1], choice [NE]
   float* xs = route_smem;
   float* z = xs + width;
   float* choice = z + NE + 1;
@@ -40,10 +40,25 @@ moe_route_kernel(const T* __restrict__ x, int width, const float* __restrict__ r
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int rows = NE + (shared_gate_w != nullptr ? 1 : 0);
+  // A row's loads go out together (a few rows per warp, each a chain of fetches otherwise); the
+  // sum's order depends on the width alone.
+  const bool vec = width % 4 == 0;
   for (int e = warp; e < rows; e += nwarps) {
     const float* w = e < NE ? router_w + (size_t)e * width : shared_gate_w;
     float acc = 0.f;
-    for (int c = lane; c < width; c += 32) acc = fmaf(w[c], xs[c], acc);
+    if (vec) {
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+      for (int c = lane * 4; c < width; c += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + c);
+        const float4 xv = *reinterpret_cast<const float4*>(xs + c);
+        a0 = fmaf(wv.x, xv.x, a0); a1 = fmaf(wv.y, xv.y, a1); a2 = fmaf(wv.z, xv.z, a2); a3 = fmaf(wv.w, xv.w, a3);
+      }
+      acc = (a0 + a1) + (a2 + a3);
+    } else {
+#pragma unroll 4
+      for (int c = lane; c < width; c += 32) acc = fmaf(w[c], xs[c], acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) z[e] = acc;
   }
@@ -100,11 +115,11 @@ extern "C" int sb_moe_route(const void* x, int dtype, int num_tokens, int width,
   if (top < 1 || top > NE || smem > 200 * 1024) return -13;
   if (dtype == SB_DTYPE_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(moe_route_kernel<float>, num_tokens, 128, smem, stream, (const float*)x, width, router_w, correction,
+    sb_launch(moe_route_kernel<float>, num_tokens, 256, smem, stream, (const float*)x, width, router_w, correction,
               shared_gate_w, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(moe_route_kernel<bf16>, num_tokens, 128, smem, stream, (const bf16*)x, width, router_w, correction,
+    sb_launch(moe_route_kernel<bf16>, num_tokens, 256, smem, stream, (const bf16*)x, width, router_w, correction,
               shared_gate_w, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
   }
   SB_LAUNCH_CHECK();
@@ -204,6 +219,23 @@ template <typename T> struct MoeTile;
 template <> struct MoeTile<bf16> { static constexpr int K = 64, LD = 72; };
 template <> struct MoeTile<float> { static constexpr int K = 32, LD = 33; };
 
+// Stages of the ring of tiles that feeds the products: bfloat16 tiles come by cp.async, up to
+// two k-steps ahead of the one being multiplied; float32 tiles are fetched as they are needed.
+template <typename T> struct MoeStages;
+template <> struct MoeStages<bf16> { static constexpr int N = 3; };
+template <> struct MoeStages<float> { static constexpr int N = 1; };
+
+template <typename T>
+constexpr size_t moe_product_smem() {
+  const size_t ring = (size_t)MoeStages<T>::N * (MOE_TILE_M + 2 * MOE_TILE_N) * MoeTile<T>::LD * sizeof(T);
+  const size_t sums = (size_t)2 * MOE_TILE_M * (MOE_TILE_N + 4) * sizeof(float);
+  return ring > sums ? ring : sums;
+}
+
+__device__ __forceinline__ void moe_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, int pair_div,
@@ -212,10 +244,11 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
                    const int* __restrict__ tile_rows, int act, T* __restrict__ out) {
   pdl_wait_block();
   pdl_launch_dependents();
-  constexpr int BK = MoeTile<T>::K, LD = MoeTile<T>::LD;
-  __shared__ __align__(32) T As[MOE_TILE_M * LD];
-  __shared__ __align__(32) T Ws[2 * MOE_TILE_N * LD];
-  __shared__ __align__(32) float Cs[2 * MOE_TILE_M * (MOE_TILE_N + 4)];
+  constexpr int BK = MoeTile<T>::K, LD = MoeTile<T>::LD, NST = MoeStages<T>::N;
+  constexpr int STAGE = (MOE_TILE_M + 2 * MOE_TILE_N) * LD;  // elements: the A tile, then the two W tiles
+  extern __shared__ __align__(128) unsigned char moe_smem[];
+  T* ring = reinterpret_cast<T*>(moe_smem);
+  float* Cs = reinterpret_cast<float*>(moe_smem);  // the sums, once the ring is done with
   __shared__ int src_row[MOE_TILE_M];
   constexpr int CLD = MOE_TILE_N + 4;
   const int e = tile_expert[blockIdx.x];
@@ -232,48 +265,62 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
   constexpr int V = 16 / sizeof(T);  // elements of a 16-byte piece
   const bool vec = K % V == 0;
 
+  // Fetches k-step k0 into a stage: 16-byte pieces where a whole one lies inside the matrix
+  // (bfloat16: asynchronously), zeros and ragged ends by plain stores.
+  auto fetch = [&](T* stage, int k0) {
+    for (int idx = threadIdx.x; idx < (MOE_TILE_M + 2 * MOE_TILE_N) * (BK / V); idx += blockDim.x) {
+      const int j = idx / (BK / V), c = (idx - j * (BK / V)) * V;
+      const T* src = nullptr;
+      if (j < MOE_TILE_M) {
+        if (src_row[j] >= 0) src = A + (size_t)src_row[j] * K;
+      } else {
+        const int w = j - MOE_TILE_M, set = w / MOE_TILE_N, jj = w - set * MOE_TILE_N;
+        const int n = n0 + (GATED ? 0 : set * MOE_TILE_N) + jj;  // output column
+        if (n < N) src = We + (size_t)(GATED ? set * second + n : n) * K;
+      }
+      T* dst = stage + j * LD + c;
+      if (src != nullptr && vec && k0 + c + V <= K) {
+        if constexpr (sizeof(T) == 2) moe_async16(dst, src + k0 + c);
+        else moe_copy16(dst, src + k0 + c);
+      } else {
+#pragma unroll
+        for (int q = 0; q < V; ++q) dst[q] = (src != nullptr && k0 + c + q < K) ? src[k0 + c + q] : from_f32<T>(0.f);
+      }
+    }
+  };
+
   [[maybe_unused]] const int warp = threadIdx.x >> 5;
   // float32: thread (ty, tx) owns rows 4 ty .. 4 ty + 3 and columns 2 tx, 2 tx + 1 of both sets
   [[maybe_unused]] const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
-  float acc[2][4][2];
+  [[maybe_unused]] float acc[2][4][2];
 #pragma unroll
   for (int s = 0; s < 2; ++s)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[s][i][0] = acc[s][i][1] = 0.f;
-  nvcuda::wmma::fragment<nvcuda::wmma::accumulator, 16, 16, 16, float> cfrag[2];
+  [[maybe_unused]] nvcuda::wmma::fragment<nvcuda::wmma::accumulator, 16, 16, 16, float> cfrag[2];
   if constexpr (sizeof(T) == 2) {
     nvcuda::wmma::fill_fragment(cfrag[0], 0.f);
     nvcuda::wmma::fill_fragment(cfrag[1], 0.f);
   }
 
-  for (int k0 = 0; k0 < K; k0 += BK) {
-    // A tile: MOE_TILE_M rows of BK
-    for (int idx = threadIdx.x; idx < MOE_TILE_M * (BK / V); idx += blockDim.x) {
-      const int r = idx / (BK / V), c = (idx - r * (BK / V)) * V;
-      const int src = src_row[r];
-      T* dst = As + r * LD + c;
-      if (src >= 0 && vec && k0 + c + V <= K) {
-        moe_copy16(dst, A + (size_t)src * K + k0 + c);
-      } else {
+  const int steps = (K + BK - 1) / BK;
+  if constexpr (NST > 1) {
 #pragma unroll
-        for (int q = 0; q < V; ++q)
-          dst[q] = (src >= 0 && k0 + c + q < K) ? A[(size_t)src * K + k0 + c + q] : from_f32<T>(0.f);
-      }
+    for (int p = 0; p < NST - 1; ++p) {
+      if (p < steps) fetch(ring + p * STAGE, p * BK);
+      asm volatile("cp.async.commit_group;\n" ::);
     }
-    // W tiles: two sets of MOE_TILE_N rows of BK
-    for (int idx = threadIdx.x; idx < 2 * MOE_TILE_N * (BK / V); idx += blockDim.x) {
-      const int j = idx / (BK / V), c = (idx - j * (BK / V)) * V;
-      const int s = j / MOE_TILE_N, jj = j - s * MOE_TILE_N;
-      const int n = n0 + (GATED ? 0 : s * MOE_TILE_N) + jj;  // output column
-      const int wrow = n < N ? (GATED ? s * second + n : n) : -1;
-      T* dst = Ws + j * LD + c;
-      if (wrow >= 0 && vec && k0 + c + V <= K) {
-        moe_copy16(dst, We + (size_t)wrow * K + k0 + c);
-      } else {
-#pragma unroll
-        for (int q = 0; q < V; ++q)
-          dst[q] = (wrow >= 0 && k0 + c + q < K) ? We[(size_t)wrow * K + k0 + c + q] : from_f32<T>(0.f);
-      }
+  }
+  for (int kt = 0; kt < steps; ++kt) {
+    const T* As = ring + (kt % NST) * STAGE;
+    const T* Ws = As + MOE_TILE_M * LD;
+    if constexpr (NST > 1) {
+      // the stage that k-step kt + NST - 1 goes to was multiplied in the step before this one
+      if (kt + NST - 1 < steps) fetch(ring + ((kt + NST - 1) % NST) * STAGE, (kt + NST - 1) * BK);
+      asm volatile("cp.async.commit_group;\n" ::);
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(NST - 1));
+    } else {
+      fetch(ring, kt * BK);
     }
     __syncthreads();
     if constexpr (sizeof(T) == 2) {
@@ -314,6 +361,7 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
     }
     __syncthreads();
   }
+  if constexpr (NST > 1) asm volatile("cp.async.wait_group 0;\n" ::);
   if constexpr (sizeof(T) == 2) {
     const int wr = warp & 3, wc = warp >> 2;
 #pragma unroll
@@ -357,8 +405,14 @@ extern "C" int sb_moe_product(const void* A, const int* row_pair, int pair_div, 
   const int per_block = gated ? MOE_TILE_N : 2 * MOE_TILE_N;
   const dim3 grid(max_tiles, (N + per_block - 1) / per_block);
 #define SB_MOE_PRODUCT(T_, G_)                                                                                  \
-  sb_launch(moe_product_kernel<T_, G_>, grid, 256, 0, stream, (const T_*)A, row_pair, pair_div, (const T_*)W,   \
-            stride, G_ ? N : MOE_TILE_N, K, N, tile_expert, tile_row0, tile_rows, act, (T_*)out)
+  do {                                                                                                          \
+    if (moe_product_smem<T_>() > 48 * 1024)                                                                     \
+      cudaFuncSetAttribute(moe_product_kernel<T_, G_>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                           (int)moe_product_smem<T_>());                                                        \
+    sb_launch(moe_product_kernel<T_, G_>, grid, 256, moe_product_smem<T_>(), stream, (const T_*)A, row_pair,    \
+              pair_div, (const T_*)W, stride, G_ ? N : MOE_TILE_N, K, N, tile_expert, tile_row0, tile_rows,     \
+              act, (T_*)out);                                                                                   \
+  } while (0)
   if (dtype == SB_DTYPE_F32) {
     if (gated) SB_MOE_PRODUCT(float, true);
     else SB_MOE_PRODUCT(float, false);

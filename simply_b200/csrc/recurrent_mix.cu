@@ -441,7 +441,7 @@ forget_scan_kernel(const T* __restrict__ pre, int row_width, const float* __rest
                    float* __restrict__ out, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
-  extern __shared__ __align__(16) float stage[];  // q [CHUNK][d], f [CHUNK][d], v [CHUNK][cols]
+  extern __shared__ __align__(16) float stage[];  // two buffers of CHUNK tokens' q [d], f [d], v [cols]
   const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
   const int rs = threadIdx.x % RS, col_local = threadIdx.x / RS;
   const int col = col0 + col_local;
@@ -452,10 +452,27 @@ forget_scan_kernel(const T* __restrict__ pre, int row_width, const float* __rest
     if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
     return;
   }
-  float* sq = stage;
-  float* sf = sq + FORGET_CHUNK * d;
-  float* sv = sf + FORGET_CHUNK * d;
   const int q_at = h * d, f_at = H * d + h * d, v_at = 2 * H * d + h * dv;
+  const int per_token = 2 * d + cols;  // q [d], f [d], v [cols] of a token, side by side in a buffer
+  const int buffer = FORGET_CHUNK * per_token;
+  // Where element idx of a chunk's inputs lies in `pre` (idx = token * per_token + r).
+  auto raw_at = [&](int base, int idx) -> const T* {
+    const int i = idx / per_token, r = idx - i * per_token;
+    const int column = r < d ? q_at + r : (r < 2 * d ? f_at + (r - d) : v_at + min(col0 + (r - 2 * d), dv - 1));
+    return pre + (size_t)(first + base + i) * row_width + column;
+  };
+  // Its value as the walk reads it: silu on q, the gate from f, v as it is.
+  auto put = [&](float* buf, int idx, float raw) {
+    const int i = idx / per_token, r = idx - i * per_token;
+    float value = raw;
+    if (r < d) {
+      value = raw * sigmoid_f32(raw);
+    } else if (r < 2 * d) {
+      const float l = lower[q_at + r - d];
+      value = l + (1.0f - l) * sigmoid_f32(raw + bias[q_at + r - d]);
+    }
+    buf[idx] = value;
+  };
   float* S = state + ((size_t)slot * H + h) * d * dv;
   float s[ROWS];
 #pragma unroll
@@ -463,27 +480,29 @@ forget_scan_kernel(const T* __restrict__ pre, int row_width, const float* __rest
     const int row = rs + RS * r;
     s[r] = (on && row < d) ? S[(size_t)row * dv + col] : 0.f;
   }
-  for (int base = 0; base < n; base += FORGET_CHUNK) {
+  {
+    const int total = min(FORGET_CHUNK, n) * per_token;
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) put(stage, idx, to_f32<T>(*raw_at(0, idx)));
+  }
+  __syncthreads();
+  // The next chunk's inputs are fetched into registers before the walk over this one and turned
+  // into the other buffer after it, so that their way from memory is hidden behind the walk.
+  constexpr int PRE = 40;
+  T ahead[PRE];
+  int which = 0;
+  for (int base = 0; base < n; base += FORGET_CHUNK, which ^= 1) {
     const int count = min(FORGET_CHUNK, n - base);
-    __syncthreads();  // the walk over the chunk before is over
-    for (int idx = threadIdx.x; idx < count * d; idx += blockDim.x) {
-      const int i = idx / d, c = idx - i * d;
-      const T* x = pre + (size_t)(first + base + i) * row_width;
-      const float pq = to_f32<T>(x[q_at + c]);
-      const float pf = to_f32<T>(x[f_at + c]) + bias[q_at + c];
-      const float l = lower[q_at + c];
-      sq[idx] = pq * sigmoid_f32(pq);
-      sf[idx] = l + (1.0f - l) * sigmoid_f32(pf);
+    const int total_next = max(min(FORGET_CHUNK, n - base - FORGET_CHUNK), 0) * per_token;
+#pragma unroll
+    for (int k = 0; k < PRE; ++k) {
+      const int idx = threadIdx.x + k * blockDim.x;
+      if (idx < total_next) ahead[k] = *raw_at(base + FORGET_CHUNK, idx);
     }
-    for (int idx = threadIdx.x; idx < count * cols; idx += blockDim.x) {
-      const int i = idx / cols, c = idx - i * cols;
-      sv[idx] = to_f32<T>(pre[(size_t)(first + base + i) * row_width + v_at + min(col0 + c, dv - 1)]);
-    }
-    __syncthreads();
+    const float* buf = stage + which * buffer;
     for (int i = 0; i < count; ++i) {
-      const float* qq = sq + i * d;
-      const float* ff = sf + i * d;
-      const float vv = sv[i * cols + min(col_local, cols - 1)];
+      const float* qq = buf + i * per_token;
+      const float* ff = qq + d;
+      const float vv = qq[2 * d + min(col_local, cols - 1)];
       float od = 0.f;
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
@@ -498,6 +517,15 @@ forget_scan_kernel(const T* __restrict__ pre, int row_width, const float* __rest
       for (int o = 1; o < RS; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
       if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = od;
     }
+    float* other = stage + (which ^ 1) * buffer;
+#pragma unroll
+    for (int k = 0; k < PRE; ++k) {
+      const int idx = threadIdx.x + k * blockDim.x;
+      if (idx < total_next) put(other, idx, to_f32<T>(ahead[k]));
+    }
+    for (int idx = threadIdx.x + PRE * blockDim.x; idx < total_next; idx += blockDim.x)
+      put(other, idx, to_f32<T>(*raw_at(base + FORGET_CHUNK, idx)));
+    __syncthreads();
   }
   if (on && first_row_of_slot(slots, b)) {
 #pragma unroll
@@ -522,7 +550,7 @@ extern "C" int sb_forget_scan(const void* pre, int row_width, int dtype, const f
   if (cols > dv) cols = dv;
   const int block = ((cols * rs + 31) / 32) * 32;
   const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
-  const size_t smem = (size_t)FORGET_CHUNK * (2 * d + cols) * sizeof(float);
+  const size_t smem = (size_t)2 * FORGET_CHUNK * (2 * d + cols) * sizeof(float);
   if (smem > 200 * 1024) return -13;
 #define SB_FORGET_V(T_, RS_, ROWS_)                                                                            \
   do {                                                                                                         \

@@ -223,7 +223,7 @@ def run(args, peaks: dict, time_decode, design: str = "generax") -> dict:
   launches = 0
   for size_name, s in SIZES.items():
     results[size_name] = {"shape": s}
-    for design, d in ((name, DICTS[name](s)) for name in PAIRS[design]):
+    for which, d in ((name, DICTS[name](s)) for name in PAIRS[design]):
       cfg = config_from_dict(d)
       ec = EngineConfig(activation_dtype="bfloat16", page_size=64, batch_size=batch, max_seq_len=context + 64,
                         max_cache_tokens=batch * (context + 64), max_num_issue_tokens=2048, intermediate_steps=1)
@@ -252,7 +252,7 @@ def run(args, peaks: dict, time_decode, design: str = "generax") -> dict:
       for sl in slots:
         engine.close_request(sl)
       engine.ops.check_errors()
-      results[size_name][design] = r
+      results[size_name][which] = r
       del engine
       torch.cuda.empty_cache()
   return {"sizes": results, "launches": launches}

@@ -177,6 +177,12 @@ class CudaOps:
     # pages of at least 64 tokens); False keeps single blocks (tests).
     self.prefill_pairs = True
     self._rounded_scales: dict[float, float] = {}
+    # Routed experts: from this many rows per expert on average (and outside graph capture) a
+    # step's experts run one by one through the products of a dense feed-forward, after one look
+    # at how many rows each got; below, and in decode graphs, the grouped kernel (csrc/moe.cu)
+    # serves them without the host.  0: always the grouped kernel.
+    self.expert_rows_for_dense_products = int(os.environ.get("SIMPLY_B200_EXPERT_DENSE_ROWS", "96"))
+    self._wide_tables: dict[tuple, torch.Tensor] = {}
     self.prefill_single_key_group = False  # True: 64-row tiles with 4 warps instead of 4 x 2 (experiments, tests)
     # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
     self.skinny_warps = 0
@@ -675,7 +681,13 @@ class CudaOps:
       except (TypeError, RuntimeError):
         pass
     if k % 8:
-      raise KernelError(f"the output layer's width {k} must be a multiple of 8 in bfloat16")
+      # A width without whole 16-byte groups: the float32 product on a float32 copy of the table.
+      key = (table.data_ptr(), tuple(table.shape))
+      wide = self._wide_tables.get(key)
+      if wide is None:
+        wide = self._wide_tables[key] = table.float().contiguous()
+      self._call("sb_gemm_f32_nt", _ptr(self.cast(x, torch.float32)), _ptr(wide), _ptr(out), r, v, k, float(cap))
+      return out
     for r0 in range(0, r, chunk):
       rows = min(chunk, r - r0)
       self._call("sb_gemm_skinny_bf16", _ptr(x[r0:]), _ptr(table), _ptr(out[r0:]), rows, v, k, 1,
@@ -976,6 +988,24 @@ class CudaOps:
                router.shape[0], top, float(scale), int(score), int(renormalize), _ptr(chosen), _ptr(weight), _ptr(gate))
     return chosen, weight, gate
 
+  def _experts_one_by_one(self, x, sorted_pair, tiles, top, gate_up, down, activation) -> torch.Tensor:
+    """The experts' products of a long prompt portion: the rows, sorted by expert, are gathered once,
+    the host reads how many each expert got (the one wait of the step), and every expert's rows go
+    through the engine's own products for a dense feed-forward (the tcgen05 kernel with the
+    activation on its sums from 129 rows, the library's product for the way down).  Returns the rows
+    of every pair in sorted order, as the grouped kernel does."""
+    expert, row0, count = tiles.cpu().numpy()
+    total = int(count[expert >= 0].sum())  # (identity experts' pairs have no row; the list's tail is unused)
+    rows_of = torch.div(sorted_pair[:total], top, rounding_mode="floor")
+    xs = self.gather_rows(x, rows_of)
+    outs = []
+    for e in np.unique(expert[expert >= 0]):
+      mine = expert == e
+      start, n = int(row0[mine].min()), int(count[mine].sum())
+      h = self.gated_linear(xs[start:start + n], gate_up[e], activation)
+      outs.append(self.linear(h, down[e]))
+    return torch.cat(outs) if len(outs) != 1 else outs[0]
+
   def mix_experts(self, x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, gate_up: torch.Tensor | None,
                   down: torch.Tensor | None, num_experts: int, activation: int, shared: torch.Tensor | None,
                   shared_gate: torch.Tensor | None) -> torch.Tensor:
@@ -996,12 +1026,16 @@ class CudaOps:
       self._call("sb_moe_group", _ptr(chosen), pairs, num_experts, max_tiles, _ptr(sorted_pair), _ptr(pos),
                  _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]))
       hidden = down.shape[2]
-      h = self._new(pairs, hidden, dtype=x.dtype)
-      self._call("sb_moe_product", _ptr(x), _ptr(sorted_pair), top, _ptr(gate_up), _code(x), 1, width, hidden,
-                 _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, activation, _ptr(h))
-      y_pair = self._new(pairs, width, dtype=x.dtype)
-      self._call("sb_moe_product", _ptr(h), None, 1, _ptr(down), _code(x), 0, hidden, width,
-                 _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, 0, _ptr(y_pair))
+      if (x.dtype == torch.bfloat16 and 0 < self.expert_rows_for_dense_products * num_experts <= pairs
+          and not torch.cuda.is_current_stream_capturing()):
+        y_pair = self._experts_one_by_one(x, sorted_pair, tiles, top, gate_up, down, activation)
+      else:
+        h = self._new(pairs, hidden, dtype=x.dtype)
+        self._call("sb_moe_product", _ptr(x), _ptr(sorted_pair), top, _ptr(gate_up), _code(x), 1, width, hidden,
+                   _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, activation, _ptr(h))
+        y_pair = self._new(pairs, width, dtype=x.dtype)
+        self._call("sb_moe_product", _ptr(h), None, 1, _ptr(down), _code(x), 0, hidden, width,
+                   _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), max_tiles, 0, _ptr(y_pair))
     else:
       pos.fill_(-1)
     if shared is not None and shared.dtype != x.dtype:

@@ -78,6 +78,12 @@ CONFIG_B = config(
 CONFIG_C = config([hgrn2(heads=2, dim=16, vdim=16), hgrn2(heads=4, dim=8, vdim=8)], [dense(ff=32), None], width=32, vocab=60)
 
 
+# Sizes without whole 16-byte groups anywhere: an odd width's worth of heads, odd recurrent heads.
+CONFIG_D = config([attention(heads=2, kv_heads=1, dim=6, dims=2, scale=0.6), hgrn2(heads=3, dim=5, vdim=7)],
+                  [moe(experts=3, identity=1, top=2, ff=10, shared=6), dense(ff=14, limit=1.0)], width=36, vocab=50,
+                  loop=(0, 2, 2))
+
+
 def weights(cfg_dict, seed=0, matrix_std=0.25, scale_std=0.2, slow=True):
   """bfloat16-representable random weights by tensor name (CPU, bfloat16)."""
   cfg = config_from_dict(cfg_dict)

@@ -209,6 +209,13 @@ def test_routing_and_the_experts_products(sizes, where):
       want[t] += a * (plain.silu_expert(x64[t:t + 1], w64, f"m.e{e}")[0] if e < experts else x64[t])
   want += plain.sigmoid(x64 @ w64["m.shared.sg"].T) * shared64
   close(got, want, dtype, f"experts {sizes}", f32=3e-5, bf16=3e-2)
+  if hasattr(ops, "expert_rows_for_dense_products"):
+    # both ways of multiplying: expert by expert through the dense products, and the grouped kernel
+    for threshold in (0, 1):
+      ops.expert_rows_for_dense_products = threshold
+      got = ops.mix_experts(x, chosen, weight, gate_up, down, experts, 1, shared, gate).float().cpu().numpy()
+      close(got, want, dtype, f"experts {sizes}, threshold {threshold}", f32=3e-5, bf16=3e-2)
+    ops.check_errors()
   # a step of one token and of three: tiles that are mostly empty
   for n in (1, 3):
     got = ops.mix_experts(x[:n].contiguous(), chosen[:n].contiguous(), weight[:n].contiguous(), gate_up, down, experts, 1,
