@@ -426,22 +426,43 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
 // The forget-gate recurrence (HGRN2): per head a matrix S [d, dv] whose rows decay by f and take in
 // (1 - f) v, read by q after the write:
 //   q = silu(pq),  f = l + (1 - l) sigmoid(pf + b),  S <- diag(f) S + (1 - f) v^T,  o = S^T q
-// `pre` [T, row_width] holds pq (H d) | pf (H d) | v (H dv) as the projection left them; the
-// activations and the gate are computed here, in float32, as a chunk of tokens is fetched.  The
-// layout of a block is the delta rule's: a column of S over RS neighbouring lanes with ROWS rows
-// each, a block per (head, sequence, tile of columns), the state written back by the slot's first row.
+// `pre` [T, row_width] holds pq (H d) | pf (H d) | v (H dv) as the projection left them.  Two
+// kernels: the inputs (activations and gates once per token, float32: qf [T, 2, H d] and v [T, H dv]),
+// and the walk, whose layout is the delta rule's: a column of S over RS neighbouring lanes with ROWS
+// rows each, a block per (head, sequence, tile of columns), q, f and v of 16 tokens at a time
+// by cp.async with the next chunk under way, the state written back by the slot's first row.  The
+// state's update is one multiply-add per row and token and does not wait for the sum that reads it.
 // ---------------------------------------------------------------------------
 #define FORGET_CHUNK 16
 
-template <typename T, int RS, int ROWS>
-__global__ void __launch_bounds__(128)
-forget_scan_kernel(const T* __restrict__ pre, int row_width, const float* __restrict__ bias,
-                   const float* __restrict__ lower, float* __restrict__ state, const int* __restrict__ cu_q,
-                   const int* __restrict__ slots, int num_slots, int H, int d, int dv, int cols,
-                   float* __restrict__ out, int* err) {
+template <typename T>
+__global__ void __launch_bounds__(256)
+forget_inputs_kernel(const T* __restrict__ pre, int row_width, const float* __restrict__ bias,
+                     const float* __restrict__ lower, int n_qf, int n_v, float* __restrict__ qf,
+                     float* __restrict__ v) {
   pdl_wait_block();
   pdl_launch_dependents();
-  extern __shared__ __align__(16) float stage[];  // two buffers of CHUNK tokens' q [d], f [d], v [cols]
+  const int t = blockIdx.x;
+  const T* x = pre + (size_t)t * row_width;
+  float* out = qf + (size_t)t * 2 * n_qf;
+  for (int c = threadIdx.x; c < n_qf; c += blockDim.x) {
+    const float pq = to_f32<T>(x[c]);
+    const float l = lower[c];
+    out[c] = pq * sigmoid_f32(pq);
+    out[n_qf + c] = l + (1.0f - l) * sigmoid_f32(to_f32<T>(x[n_qf + c]) + bias[c]);
+  }
+  for (int c = threadIdx.x; c < n_v; c += blockDim.x) v[(size_t)t * n_v + c] = to_f32<T>(x[2 * n_qf + c]);
+}
+
+template <int RS, int ROWS, bool VEC>
+__global__ void __launch_bounds__(128)
+forget_scan_kernel(const float* __restrict__ qf, const float* __restrict__ v, float* __restrict__ state,
+                   const int* __restrict__ cu_q, const int* __restrict__ slots, int num_slots, int H, int d, int dv,
+                   int cols, float* __restrict__ out, int* err) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  // Two buffers of: q [CHUNK][d], f [CHUNK][d], v [CHUNK][cols_pad].
+  extern __shared__ __align__(16) float stage[];
   const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
   const int rs = threadIdx.x % RS, col_local = threadIdx.x / RS;
   const int col = col0 + col_local;
@@ -452,96 +473,119 @@ forget_scan_kernel(const T* __restrict__ pre, int row_width, const float* __rest
     if (threadIdx.x == 0) atomicOr(err, SB_ERR_BAD_SLOT);
     return;
   }
-  const int q_at = h * d, f_at = H * d + h * d, v_at = 2 * H * d + h * dv;
-  const int per_token = 2 * d + cols;  // q [d], f [d], v [cols] of a token, side by side in a buffer
-  const int buffer = FORGET_CHUNK * per_token;
-  // Where element idx of a chunk's inputs lies in `pre` (idx = token * per_token + r).
-  auto raw_at = [&](int base, int idx) -> const T* {
-    const int i = idx / per_token, r = idx - i * per_token;
-    const int column = r < d ? q_at + r : (r < 2 * d ? f_at + (r - d) : v_at + min(col0 + (r - 2 * d), dv - 1));
-    return pre + (size_t)(first + base + i) * row_width + column;
-  };
-  // Its value as the walk reads it: silu on q, the gate from f, v as it is.
-  auto put = [&](float* buf, int idx, float raw) {
-    const int i = idx / per_token, r = idx - i * per_token;
-    float value = raw;
-    if (r < d) {
-      value = raw * sigmoid_f32(raw);
-    } else if (r < 2 * d) {
-      const float l = lower[q_at + r - d];
-      value = l + (1.0f - l) * sigmoid_f32(raw + bias[q_at + r - d]);
+  const int cols_pad = (cols + 3) & ~3;
+  const int buffer = FORGET_CHUNK * (2 * d + cols_pad);
+  const int n_qf = H * d;
+
+  auto issue = [&](int which, int base) {
+    float* buf = stage + which * buffer;
+    const int count = min(FORGET_CHUNK, n - base);
+    if (VEC) {
+      const int d4 = d >> 2;
+      for (int idx = threadIdx.x; idx < count * 2 * d4; idx += blockDim.x) {
+        const int i = idx / (2 * d4), rem = idx - i * 2 * d4, kind = rem / d4, c = (rem - kind * d4) * 4;
+        scan_copy16(buf + (kind * FORGET_CHUNK + i) * d + c,
+                    qf + ((size_t)(first + base + i) * 2 + kind) * n_qf + h * d + c);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < count * 2 * d; idx += blockDim.x) {
+        const int i = idx / (2 * d), rem = idx - i * 2 * d, kind = rem / d, c = rem - kind * d;
+        scan_copy4(buf + (kind * FORGET_CHUNK + i) * d + c,
+                   qf + ((size_t)(first + base + i) * 2 + kind) * n_qf + h * d + c);
+      }
     }
-    buf[idx] = value;
+    float* bv = buf + 2 * FORGET_CHUNK * d;
+    for (int idx = threadIdx.x; idx < count * cols; idx += blockDim.x) {
+      const int i = idx / cols, c = idx - i * cols;
+      scan_copy4(bv + i * cols_pad + c, v + ((size_t)(first + base + i) * H + h) * dv + min(col0 + c, dv - 1));
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
   };
+
+  if (n > 0) issue(0, 0);
   float* S = state + ((size_t)slot * H + h) * d * dv;
   float s[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
-    const int row = rs + RS * r;
+    const int row = VEC ? 4 * (rs + RS * (r >> 2)) + (r & 3) : rs + RS * r;
     s[r] = (on && row < d) ? S[(size_t)row * dv + col] : 0.f;
   }
-  {
-    const int total = min(FORGET_CHUNK, n) * per_token;
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) put(stage, idx, to_f32<T>(*raw_at(0, idx)));
-  }
-  __syncthreads();
-  // The next chunk's inputs are fetched into registers before the walk over this one and turned
-  // into the other buffer after it, so that their way from memory is hidden behind the walk.
-  constexpr int PRE = 40;
-  T ahead[PRE];
   int which = 0;
   for (int base = 0; base < n; base += FORGET_CHUNK, which ^= 1) {
     const int count = min(FORGET_CHUNK, n - base);
-    const int total_next = max(min(FORGET_CHUNK, n - base - FORGET_CHUNK), 0) * per_token;
-#pragma unroll
-    for (int k = 0; k < PRE; ++k) {
-      const int idx = threadIdx.x + k * blockDim.x;
-      if (idx < total_next) ahead[k] = *raw_at(base + FORGET_CHUNK, idx);
+    if (base + FORGET_CHUNK < n) {
+      issue(which ^ 1, base + FORGET_CHUNK);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
     }
+    __syncthreads();
     const float* buf = stage + which * buffer;
     for (int i = 0; i < count; ++i) {
-      const float* qq = buf + i * per_token;
-      const float* ff = qq + d;
-      const float vv = qq[2 * d + min(col_local, cols - 1)];
-      float od = 0.f;
+      const float* qq = buf + i * d;
+      const float* ff = buf + (FORGET_CHUNK + i) * d;
+      const float vv = buf[2 * FORGET_CHUNK * d + i * cols_pad + min(col_local, cols - 1)];
+      float od;
+      if constexpr (VEC) {
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        const int row = rs + RS * r;
-        if (row < d) {
-          const float f = ff[row];
-          s[r] = fmaf(f, s[r], (1.0f - f) * vv);
-          od = fmaf(s[r], qq[row], od);
+        for (int r = 0; r < ROWS / 4; ++r) {
+          const int at = rs + RS * r;
+          if (4 * at < d) {
+            const float4 f4 = reinterpret_cast<const float4*>(ff)[at];
+            const float4 q4 = reinterpret_cast<const float4*>(qq)[at];
+            s[4 * r] = fmaf(f4.x, s[4 * r], (1.0f - f4.x) * vv); o0 = fmaf(s[4 * r], q4.x, o0);
+            s[4 * r + 1] = fmaf(f4.y, s[4 * r + 1], (1.0f - f4.y) * vv); o1 = fmaf(s[4 * r + 1], q4.y, o1);
+            s[4 * r + 2] = fmaf(f4.z, s[4 * r + 2], (1.0f - f4.z) * vv); o2 = fmaf(s[4 * r + 2], q4.z, o2);
+            s[4 * r + 3] = fmaf(f4.w, s[4 * r + 3], (1.0f - f4.w) * vv); o3 = fmaf(s[4 * r + 3], q4.w, o3);
+          }
+        }
+        od = (o0 + o1) + (o2 + o3);
+      } else {
+        od = 0.f;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          const int row = rs + RS * r;
+          if (row < d) {
+            const float f = ff[row];
+            s[r] = fmaf(f, s[r], (1.0f - f) * vv);
+            od = fmaf(s[r], qq[row], od);
+          }
         }
       }
 #pragma unroll
       for (int o = 1; o < RS; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
       if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = od;
     }
-    float* other = stage + (which ^ 1) * buffer;
-#pragma unroll
-    for (int k = 0; k < PRE; ++k) {
-      const int idx = threadIdx.x + k * blockDim.x;
-      if (idx < total_next) put(other, idx, to_f32<T>(ahead[k]));
-    }
-    for (int idx = threadIdx.x + PRE * blockDim.x; idx < total_next; idx += blockDim.x)
-      put(other, idx, to_f32<T>(*raw_at(base + FORGET_CHUNK, idx)));
-    __syncthreads();
+    __syncthreads();  // the buffer is filled again two chunks on
   }
   if (on && first_row_of_slot(slots, b)) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
-      const int row = rs + RS * r;
+      const int row = VEC ? 4 * (rs + RS * (r >> 2)) + (r & 3) : rs + RS * r;
       if (row < d) S[(size_t)row * dv + col] = s[r];
     }
   }
 }
 
+// scratch: float32 [T, 2 H d + H dv] for the inputs.
 extern "C" int sb_forget_scan(const void* pre, int row_width, int dtype, const float* bias, const float* lower,
-                              float* state, const int* cu_q, const int* slots, int num_seqs, int num_slots, int H,
-                              int d, int dv, int max_q_len, float* out, int* err, cudaStream_t stream) {
-  if (num_seqs == 0) return 0;
+                              float* state, const int* cu_q, const int* slots, int num_tokens, int num_seqs,
+                              int num_slots, int H, int d, int dv, int max_q_len, float* scratch, float* out,
+                              int* err, cudaStream_t stream) {
+  if (num_seqs == 0 || num_tokens == 0) return 0;
   if (d <= 0 || d > 32 * 32 || dv <= 0 || H <= 0) return -13;
-  const int rows = d <= 8 * 32 ? 8 : 32;
+  float* qf = scratch;
+  float* v = scratch + (size_t)num_tokens * 2 * H * d;
+  if (dtype == SB_DTYPE_F32)
+    sb_launch(forget_inputs_kernel<float>, num_tokens, 256, 0, stream, (const float*)pre, row_width, bias, lower,
+              H * d, H * dv, qf, v);
+  else
+    sb_launch(forget_inputs_kernel<bf16>, num_tokens, 256, 0, stream, (const bf16*)pre, row_width, bias, lower,
+              H * d, H * dv, qf, v);
+  SB_LAUNCH_CHECK();
+  const bool vec = d % 4 == 0;
+  const int rows = (vec && d <= 8 * 32) ? 8 : 32;
   int rs = 1;
   while (rs * rows < d) rs <<= 1;
   const int threads = max_q_len >= 64 ? 128 : 64;
@@ -550,25 +594,21 @@ extern "C" int sb_forget_scan(const void* pre, int row_width, int dtype, const f
   if (cols > dv) cols = dv;
   const int block = ((cols * rs + 31) / 32) * 32;
   const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
-  const size_t smem = (size_t)2 * FORGET_CHUNK * (2 * d + cols) * sizeof(float);
+  const size_t smem = (size_t)2 * FORGET_CHUNK * (2 * d + ((cols + 3) & ~3)) * sizeof(float);
   if (smem > 200 * 1024) return -13;
-#define SB_FORGET_V(T_, RS_, ROWS_)                                                                            \
+#define SB_FORGET_V(RS_, ROWS_, VEC_)                                                                          \
   do {                                                                                                         \
     if (smem > 48 * 1024)                                                                                      \
-      cudaFuncSetAttribute(forget_scan_kernel<T_, RS_, ROWS_>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+      cudaFuncSetAttribute(forget_scan_kernel<RS_, ROWS_, VEC_>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                            (int)smem);                                                                         \
-    sb_launch(forget_scan_kernel<T_, RS_, ROWS_>, grid, block, smem, stream, (const T_*)pre, row_width, bias,  \
-              lower, state, cu_q, slots, num_slots, H, d, dv, cols, out, err);                                 \
+    sb_launch(forget_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, (const float*)qf,               \
+              (const float*)v, state, cu_q, slots, num_slots, H, d, dv, cols, out, err);                       \
   } while (0)
-#define SB_FORGET(RS_)                                      \
-  do {                                                      \
-    if (dtype == SB_DTYPE_F32) {                            \
-      if (rows == 8) SB_FORGET_V(float, RS_, 8);            \
-      else SB_FORGET_V(float, RS_, 32);                     \
-    } else {                                                \
-      if (rows == 8) SB_FORGET_V(bf16, RS_, 8);             \
-      else SB_FORGET_V(bf16, RS_, 32);                      \
-    }                                                       \
+#define SB_FORGET(RS_)                                \
+  do {                                                \
+    if (rows == 8) SB_FORGET_V(RS_, 8, true);         \
+    else if (vec) SB_FORGET_V(RS_, 32, true);         \
+    else SB_FORGET_V(RS_, 32, false);                 \
   } while (0)
   switch (rs) {
     case 1: SB_FORGET(1); break;

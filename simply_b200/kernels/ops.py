@@ -269,7 +269,7 @@ class CudaOps:
                                      c_int, c_int, c_int, c_int, c_void, c_void],
         "sb_sigmoid_gate": [c_void, c_void, c_int, c_int, c_int, c_int, c_void],
         "sb_forget_scan": [c_void, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_int, c_int, c_int, c_int,
-                           c_int, c_int, c_void, c_void, c_void],
+                           c_int, c_int, c_int, c_void, c_void, c_void, c_void],
         "sb_moe_route": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_int, c_int, c_float, c_int, c_int,
                          c_void, c_void, c_void, c_void],
         "sb_moe_group": [c_void, c_int, c_int, c_int, c_void, c_void, c_void, c_void, c_void, c_void],
@@ -966,10 +966,13 @@ class CudaOps:
                        ctx: Any, *, num_heads: int, head_dim: int, value_dim: int) -> torch.Tensor:
     """pre [T, q | f | v] as projected -> float32 o [T, heads, value_dim]; walks every sequence's
     tokens through its state [slots, heads, head_dim, value_dim] (csrc/recurrent_mix.cu)."""
-    out = self._new(pre.shape[0], num_heads, value_dim, dtype=torch.float32)
+    t = pre.shape[0]
+    out = self._new(t, num_heads, value_dim, dtype=torch.float32)
+    scratch = self._new(t, num_heads * (2 * head_dim + value_dim), dtype=torch.float32)  # activations, gates, values
     self._call("sb_forget_scan", _ptr(pre), pre.shape[1], _code(pre), _ptr(bias), _ptr(lower), _ptr(state),
-               _ptr(ctx.cu_q), _ptr(ctx.slots), ctx.num_seqs, state.shape[0], num_heads, head_dim, value_dim,
-               ctx.max_q_len, _ptr(out), _ptr(self.err))
+               _ptr(ctx.cu_q), _ptr(ctx.slots), t, ctx.num_seqs, state.shape[0], num_heads, head_dim, value_dim,
+               ctx.max_q_len, _ptr(scratch), _ptr(out), _ptr(self.err))
+    self.launches += 1
     return out
 
   # ---- routed experts -------------------------------------------------------------

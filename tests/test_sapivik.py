@@ -278,3 +278,13 @@ def test_model_folder_and_the_step_function_on_it(tmp_path):
   got = engine.step_raw([StepEntry(slot, toks, tuple(range(len(toks))))]).numpy()
   engine.close_request(slot)
   sx.check_close(got, plain.forward(sx.CONFIG_B, w, toks), "float32", "a written folder")
+
+
+def test_the_preset_generates_from_random_weights():
+  from simply_b200.config import preset
+  cfg = preset("sapivik-tiny")
+  assert cfg.architecture == "Sapivik" and cfg.loop == (0, 2, 2)
+  ec = EngineConfig(activation_dtype="float32", page_size=8, batch_size=2, max_seq_len=64, use_cuda_graphs=False)
+  engine = Engine.from_config(cfg, 1, ec, matrix_std=0.2, ops=ReferenceOps(torch.float32), device="cpu")
+  results = engine.generate([[1, 2, 3], [7]], SamplingParams(temperature=0.0, max_decode_steps=5))
+  assert [len(r.output_token_ids) for r in results] == [5, 5]
