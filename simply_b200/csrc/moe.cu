@@ -265,26 +265,39 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
   constexpr int V = 16 / sizeof(T);  // elements of a 16-byte piece
   const bool vec = K % V == 0;
 
-  // Fetches k-step k0 into a stage: 16-byte pieces where a whole one lies inside the matrix
-  // (bfloat16: asynchronously), zeros and ragged ends by plain stores.
+  // The ring starts as zeros: rows of the tile that hold no pair, and weight rows beyond the
+  // matrix, are never fetched and stay zero (a step of single tokens has a few rows per tile).
+  for (int i = threadIdx.x; i < (int)(NST * STAGE * sizeof(T) / 16); i += blockDim.x)
+    reinterpret_cast<uint4*>(moe_smem)[i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+
+  // Fetches k-step k0 into a stage: the tile's `rows` rows of A, then the two sets of weight rows;
+  // 16-byte pieces where a whole one lies inside the matrix (bfloat16: asynchronously), the ragged
+  // end of K by plain stores with zeros behind it.
+  constexpr int PIECES = BK / V;
   auto fetch = [&](T* stage, int k0) {
-    for (int idx = threadIdx.x; idx < (MOE_TILE_M + 2 * MOE_TILE_N) * (BK / V); idx += blockDim.x) {
-      const int j = idx / (BK / V), c = (idx - j * (BK / V)) * V;
-      const T* src = nullptr;
-      if (j < MOE_TILE_M) {
-        if (src_row[j] >= 0) src = A + (size_t)src_row[j] * K;
+    const int a_pieces = rows * PIECES;
+    for (int idx = threadIdx.x; idx < a_pieces + 2 * MOE_TILE_N * PIECES; idx += blockDim.x) {
+      int j;
+      const T* src;
+      if (idx < a_pieces) {
+        j = idx / PIECES;
+        src = A + (size_t)src_row[j] * K;
       } else {
-        const int w = j - MOE_TILE_M, set = w / MOE_TILE_N, jj = w - set * MOE_TILE_N;
+        const int w = (idx - a_pieces) / PIECES, set = w / MOE_TILE_N, jj = w - set * MOE_TILE_N;
         const int n = n0 + (GATED ? 0 : set * MOE_TILE_N) + jj;  // output column
-        if (n < N) src = We + (size_t)(GATED ? set * second + n : n) * K;
+        if (n >= N) continue;
+        j = MOE_TILE_M + w;
+        src = We + (size_t)(GATED ? set * second + n : n) * K;
       }
+      const int c = (idx % PIECES) * V;
       T* dst = stage + j * LD + c;
-      if (src != nullptr && vec && k0 + c + V <= K) {
+      if (vec && k0 + c + V <= K) {
         if constexpr (sizeof(T) == 2) moe_async16(dst, src + k0 + c);
         else moe_copy16(dst, src + k0 + c);
       } else {
 #pragma unroll
-        for (int q = 0; q < V; ++q) dst[q] = (src != nullptr && k0 + c + q < K) ? src[k0 + c + q] : from_f32<T>(0.f);
+        for (int q = 0; q < V; ++q) dst[q] = k0 + c + q < K ? src[k0 + c + q] : from_f32<T>(0.f);
       }
     }
   };
@@ -326,6 +339,7 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
     if constexpr (sizeof(T) == 2) {
       using namespace nvcuda;
       const int wr = warp & 3, wc = warp >> 2;
+      if (wr * 16 < rows)  // (a warp whose 16 rows hold no pair has nothing to multiply)
 #pragma unroll
       for (int kk = 0; kk < BK; kk += 16) {
         wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;

@@ -521,6 +521,8 @@ forget_scan_kernel(const float* __restrict__ qf, const float* __restrict__ v, fl
     }
     __syncthreads();
     const float* buf = stage + which * buffer;
+    // (unrolled: a token's sum over lanes does not hold up the next token's update of the state)
+#pragma unroll 4
     for (int i = 0; i < count; ++i) {
       const float* qq = buf + i * d;
       const float* ff = buf + (FORGET_CHUNK + i) * d;

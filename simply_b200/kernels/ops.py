@@ -181,7 +181,7 @@ class CudaOps:
     # step's experts run one by one through the products of a dense feed-forward, after one look
     # at how many rows each got; below, and in decode graphs, the grouped kernel (csrc/moe.cu)
     # serves them without the host.  0: always the grouped kernel.
-    self.expert_rows_for_dense_products = int(os.environ.get("SIMPLY_B200_EXPERT_DENSE_ROWS", "96"))
+    self.expert_rows_for_dense_products = int(os.environ.get("SIMPLY_B200_EXPERT_DENSE_ROWS", "384"))
     self._wide_tables: dict[tuple, torch.Tensor] = {}
     self.prefill_single_key_group = False  # True: 64-row tiles with 4 warps instead of 4 x 2 (experiments, tests)
     # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
