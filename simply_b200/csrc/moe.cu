@@ -273,31 +273,43 @@ moe_product_kernel(const T* __restrict__ A, const int* __restrict__ row_pair, in
 
   // Fetches k-step k0 into a stage: the tile's `rows` rows of A, then the two sets of weight rows;
   // 16-byte pieces where a whole one lies inside the matrix (bfloat16: asynchronously), the ragged
-  // end of K by plain stores with zeros behind it.
+  // end of K by plain stores with zeros behind it.  A thread fetches the same pieces in every
+  // k-step: where they come from and go to is worked out once.
   constexpr int PIECES = BK / V;
-  auto fetch = [&](T* stage, int k0) {
+  constexpr int MINE = (MOE_TILE_M + 2 * MOE_TILE_N) * PIECES / 256;  // pieces per thread (256 threads)
+  const T* piece_src[MINE];
+  int piece_dst[MINE], piece_col[MINE];
+#pragma unroll
+  for (int p = 0; p < MINE; ++p) {
+    const int idx = threadIdx.x + p * 256;
     const int a_pieces = rows * PIECES;
-    for (int idx = threadIdx.x; idx < a_pieces + 2 * MOE_TILE_N * PIECES; idx += blockDim.x) {
-      int j;
-      const T* src;
-      if (idx < a_pieces) {
-        j = idx / PIECES;
-        src = A + (size_t)src_row[j] * K;
-      } else {
-        const int w = (idx - a_pieces) / PIECES, set = w / MOE_TILE_N, jj = w - set * MOE_TILE_N;
-        const int n = n0 + (GATED ? 0 : set * MOE_TILE_N) + jj;  // output column
-        if (n >= N) continue;
-        j = MOE_TILE_M + w;
-        src = We + (size_t)(GATED ? set * second + n : n) * K;
-      }
-      const int c = (idx % PIECES) * V;
-      T* dst = stage + j * LD + c;
+    piece_src[p] = nullptr;
+    piece_col[p] = (idx % PIECES) * V;
+    int j = 0;
+    if (idx < a_pieces) {
+      j = idx / PIECES;
+      piece_src[p] = A + (size_t)src_row[j] * K;
+    } else if (idx < a_pieces + 2 * MOE_TILE_N * PIECES) {
+      const int w = (idx - a_pieces) / PIECES, set = w / MOE_TILE_N, jj = w - set * MOE_TILE_N;
+      const int n = n0 + (GATED ? 0 : set * MOE_TILE_N) + jj;  // output column
+      j = MOE_TILE_M + w;
+      if (n < N) piece_src[p] = We + (size_t)(GATED ? set * second + n : n) * K;
+    }
+    piece_dst[p] = j * LD + piece_col[p];
+  }
+  auto fetch = [&](T* stage, int k0) {
+#pragma unroll
+    for (int p = 0; p < MINE; ++p) {
+      if (piece_src[p] == nullptr) continue;
+      const int c = piece_col[p];
+      T* dst = stage + piece_dst[p];
+      const T* src = piece_src[p] + k0 + c;
       if (vec && k0 + c + V <= K) {
-        if constexpr (sizeof(T) == 2) moe_async16(dst, src + k0 + c);
-        else moe_copy16(dst, src + k0 + c);
+        if constexpr (sizeof(T) == 2) moe_async16(dst, src);
+        else moe_copy16(dst, src);
       } else {
 #pragma unroll
-        for (int q = 0; q < V; ++q) dst[q] = k0 + c + q < K ? src[k0 + c + q] : from_f32<T>(0.f);
+        for (int q = 0; q < V; ++q) dst[q] = k0 + c + q < K ? src[q] : from_f32<T>(0.f);
       }
     }
   };
