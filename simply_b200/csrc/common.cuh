@@ -169,6 +169,22 @@ inline cudaError_t sb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return sb_launch_level(1, kernel, grid, block, smem, stream, args...);
 }
 
+// A kernel that must not start early: one that runs long on fewer blocks than the GPU holds.
+// Launched early, its blocks take whatever room the kernel before it frees first and end up
+// several to an SM with other SMs empty, and the most crowded SM sets its time (a walk over 2,048
+// tokens on 256 blocks took 1.19 ms that way and 0.71 ms launched plainly).
+template <typename... KArgs, typename... Args>
+inline cudaError_t sb_launch_plain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                   Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  config.numAttrs = 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 // A kernel that fetches data no earlier kernel writes (weights) before it waits for its inputs.
 template <typename... KArgs, typename... Args>
 inline cudaError_t sb_launch_early(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

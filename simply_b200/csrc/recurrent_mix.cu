@@ -399,8 +399,12 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
     if (smem > 48 * 1024)                                                                                     \
       cudaFuncSetAttribute(delta_scan_kernel<RS_, ROWS_, VEC_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                                        \
-    sb_launch(delta_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, q, k, v, decay, beta, state,   \
-              cu_q, slots, num_slots, G, H, d, dv, cols, chunk, out, err);                                           \
+    if (long_walk)                                                                                            \
+      sb_launch_plain(delta_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, q, k, v, decay, beta,   \
+                      state, cu_q, slots, num_slots, G, H, d, dv, cols, chunk, out, err);                     \
+    else                                                                                                      \
+      sb_launch(delta_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, q, k, v, decay, beta, state, \
+                cu_q, slots, num_slots, G, H, d, dv, cols, chunk, out, err);                                  \
   } while (0)
 #define SB_SCAN(RS_)                                  \
   do {                                                \
@@ -603,8 +607,12 @@ extern "C" int sb_forget_scan(const void* pre, int row_width, int dtype, const f
     if (smem > 48 * 1024)                                                                                      \
       cudaFuncSetAttribute(forget_scan_kernel<RS_, ROWS_, VEC_>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                            (int)smem);                                                                         \
-    sb_launch(forget_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, (const float*)qf,               \
-              (const float*)v, state, cu_q, slots, num_slots, H, d, dv, cols, out, err);                       \
+    if (max_q_len >= 64)                                                                                       \
+      sb_launch_plain(forget_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, (const float*)qf,       \
+                      (const float*)v, state, cu_q, slots, num_slots, H, d, dv, cols, out, err);               \
+    else                                                                                                       \
+      sb_launch(forget_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, (const float*)qf,             \
+                (const float*)v, state, cu_q, slots, num_slots, H, d, dv, cols, out, err);                     \
   } while (0)
 #define SB_FORGET(RS_)                                \
   do {                                                \
