@@ -1029,8 +1029,9 @@ class CudaOps:
       self._call("sb_moe_group", _ptr(chosen), pairs, num_experts, max_tiles, _ptr(sorted_pair), _ptr(pos),
                  _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]))
       hidden = down.shape[2]
+      # (whole 16-byte groups per row, so that an expert's slice of the rows starts on a boundary)
       if (x.dtype == torch.bfloat16 and 0 < self.expert_rows_for_dense_products * num_experts <= pairs
-          and not torch.cuda.is_current_stream_capturing()):
+          and width % 8 == 0 and hidden % 8 == 0 and not torch.cuda.is_current_stream_capturing()):
         y_pair = self._experts_one_by_one(x, sorted_pair, tiles, top, gate_up, down, activation)
       else:
         h = self._new(pairs, hidden, dtype=x.dtype)
