@@ -24,7 +24,7 @@
 // route: one block per token.
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 moe_route_kernel(const T* __restrict__ x, int width, const float* __restrict__ router_w,
                  const float* __restrict__ correction, const float* __restrict__ shared_gate_w, int NE, int top,
                  float scale, int score_fn, int renormalize, int* __restrict__ chosen, float* __restrict__ weight,
@@ -113,13 +113,17 @@ extern "C" int sb_moe_route(const void* x, int dtype, int num_tokens, int width,
   if (num_tokens == 0) return 0;
   const size_t smem = ((size_t)width + 2 * NE + 1) * sizeof(float);
   if (top < 1 || top > NE || smem > 200 * 1024) return -13;
+  // A warp per router row where a block can hold them (at least 8, at most 32 warps): a row's
+  // fetches are then one round for all rows instead of one round after the other.
+  int warps = NE + (shared_gate_w != nullptr ? 1 : 0);
+  warps = warps < 8 ? 8 : (warps > 32 ? 32 : warps);
   if (dtype == SB_DTYPE_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(moe_route_kernel<float>, num_tokens, 256, smem, stream, (const float*)x, width, router_w, correction,
+    sb_launch(moe_route_kernel<float>, num_tokens, 32 * warps, smem, stream, (const float*)x, width, router_w, correction,
               shared_gate_w, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
   } else {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sb_launch(moe_route_kernel<bf16>, num_tokens, 256, smem, stream, (const bf16*)x, width, router_w, correction,
+    sb_launch(moe_route_kernel<bf16>, num_tokens, 32 * warps, smem, stream, (const bf16*)x, width, router_w, correction,
               shared_gate_w, NE, top, scale, score_fn, renormalize, chosen, weight, shared_gate);
   }
   SB_LAUNCH_CHECK();
@@ -452,7 +456,7 @@ extern "C" int sb_moe_product(const void* A, const int* row_pair, int pair_div, 
 }
 
 // ---------------------------------------------------------------------------
-// combine: one block per token.
+// combine: a block per token and slice of columns.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -462,9 +466,11 @@ moe_combine_kernel(const T* __restrict__ x, const T* __restrict__ y_pair, const 
                    T* __restrict__ out) {
   pdl_wait_block();
   pdl_launch_dependents();
+  // Grid (token, slice of 256 columns): one column per thread.
   const int t = blockIdx.x;
   const float sg = shared == nullptr ? 0.f : (shared_gate != nullptr ? shared_gate[t] : 1.0f);
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c < width) {
     float acc = 0.f;
     for (int j = 0; j < top; ++j) {
       const int p = t * top + j;
@@ -481,11 +487,12 @@ extern "C" int sb_moe_combine(const void* x, const void* y_pair, int dtype, cons
                               const int* pos_of_pair, const void* shared, const float* shared_gate, int E, int top,
                               int num_tokens, int width, void* out, cudaStream_t stream) {
   if (num_tokens == 0) return 0;
+  const dim3 grid((unsigned)num_tokens, (unsigned)((width + 255) / 256));
   if (dtype == SB_DTYPE_F32)
-    sb_launch(moe_combine_kernel<float>, num_tokens, 256, 0, stream, (const float*)x, (const float*)y_pair, chosen,
+    sb_launch(moe_combine_kernel<float>, grid, 256, 0, stream, (const float*)x, (const float*)y_pair, chosen,
               weight, pos_of_pair, (const float*)shared, shared_gate, E, top, width, (float*)out);
   else
-    sb_launch(moe_combine_kernel<bf16>, num_tokens, 256, 0, stream, (const bf16*)x, (const bf16*)y_pair, chosen,
+    sb_launch(moe_combine_kernel<bf16>, grid, 256, 0, stream, (const bf16*)x, (const bf16*)y_pair, chosen,
               weight, pos_of_pair, (const bf16*)shared, shared_gate, E, top, width, (bf16*)out);
   SB_LAUNCH_CHECK();
   return 0;

@@ -446,20 +446,22 @@ forget_inputs_kernel(const T* __restrict__ pre, int row_width, const float* __re
                      float* __restrict__ v) {
   pdl_wait_block();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
+  // Grid (token, slice of 256 channels): one channel per thread, so that a step of a few tokens
+  // is many short blocks rather than a few that loop.
+  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
   const T* x = pre + (size_t)t * row_width;
   float* out = qf + (size_t)t * 2 * n_qf;
-  for (int c = threadIdx.x; c < n_qf; c += blockDim.x) {
+  if (c < n_qf) {
     const float pq = to_f32<T>(x[c]);
     const float l = lower[c];
     out[c] = pq * sigmoid_f32(pq);
     out[n_qf + c] = l + (1.0f - l) * sigmoid_f32(to_f32<T>(x[n_qf + c]) + bias[c]);
   }
-  for (int c = threadIdx.x; c < n_v; c += blockDim.x) v[(size_t)t * n_v + c] = to_f32<T>(x[2 * n_qf + c]);
+  if (c < n_v) v[(size_t)t * n_v + c] = to_f32<T>(x[2 * n_qf + c]);
 }
 
 template <int RS, int ROWS, bool VEC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 forget_scan_kernel(const float* __restrict__ qf, const float* __restrict__ v, float* __restrict__ state,
                    const int* __restrict__ cu_q, const int* __restrict__ slots, int num_slots, int H, int d, int dv,
                    int cols, float* __restrict__ out, int* err) {
@@ -583,18 +585,23 @@ extern "C" int sb_forget_scan(const void* pre, int row_width, int dtype, const f
   if (d <= 0 || d > 32 * 32 || dv <= 0 || H <= 0) return -13;
   float* qf = scratch;
   float* v = scratch + (size_t)num_tokens * 2 * H * d;
+  const int widest = H * d > H * dv ? H * d : H * dv;
+  const dim3 in_grid((unsigned)num_tokens, (unsigned)((widest + 255) / 256));
   if (dtype == SB_DTYPE_F32)
-    sb_launch(forget_inputs_kernel<float>, num_tokens, 256, 0, stream, (const float*)pre, row_width, bias, lower,
+    sb_launch(forget_inputs_kernel<float>, in_grid, 256, 0, stream, (const float*)pre, row_width, bias, lower,
               H * d, H * dv, qf, v);
   else
-    sb_launch(forget_inputs_kernel<bf16>, num_tokens, 256, 0, stream, (const bf16*)pre, row_width, bias, lower,
+    sb_launch(forget_inputs_kernel<bf16>, in_grid, 256, 0, stream, (const bf16*)pre, row_width, bias, lower,
               H * d, H * dv, qf, v);
   SB_LAUNCH_CHECK();
   const bool vec = d % 4 == 0;
   const int rows = (vec && d <= 8 * 32) ? 8 : 32;
   int rs = 1;
   while (rs * rows < d) rs <<= 1;
-  const int threads = max_q_len >= 64 ? 128 : 64;
+  // Long walks: blocks of 128 threads (more blocks, each a chain of its own).  Steps of a few tokens
+  // read and write the state and little else: 256 threads, so that a block's columns of a state row
+  // are whole 32-byte sectors (16 columns of a row for heads of 128 channels).
+  const int threads = max_q_len >= 64 ? 128 : 256;
   int cols = threads / rs;
   if (cols < 1) cols = 1;
   if (cols > dv) cols = dv;
