@@ -438,6 +438,7 @@ extern "C" int sb_delta_scan(const float* q, const float* k, const float* v, con
 // state's update is one multiply-add per row and token and does not wait for the sum that reads it.
 // ---------------------------------------------------------------------------
 #define FORGET_CHUNK 16
+#define FORGET_TOGETHER 8  // tokens whose updates and sums are interleaved (divides the chunk)
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -464,10 +465,10 @@ template <int RS, int ROWS, bool VEC>
 __global__ void __launch_bounds__(256)
 forget_scan_kernel(const float* __restrict__ qf, const float* __restrict__ v, float* __restrict__ state,
                    const int* __restrict__ cu_q, const int* __restrict__ slots, int num_slots, int H, int d, int dv,
-                   int cols, float* __restrict__ out, int* err) {
+                   int cols, int nbuf, float* __restrict__ out, int* err) {
   pdl_wait_block();
   pdl_launch_dependents();
-  // Two buffers of: q [CHUNK][d], f [CHUNK][d], v [CHUNK][cols_pad].
+  // A ring of nbuf (2 or 4) buffers of: q [CHUNK][d], f [CHUNK][d], v [CHUNK][cols_pad].
   extern __shared__ __align__(16) float stage[];
   const int h = blockIdx.x, b = blockIdx.y, col0 = blockIdx.z * cols;
   const int rs = threadIdx.x % RS, col_local = threadIdx.x / RS;
@@ -508,7 +509,12 @@ forget_scan_kernel(const float* __restrict__ qf, const float* __restrict__ v, fl
     asm volatile("cp.async.commit_group;\n" ::);
   };
 
-  if (n > 0) issue(0, 0);
+  // The walk over a chunk is shorter than a chunk's way from memory (every column tile of a head
+  // fetches the head's q and f): nbuf - 1 chunks are under way at any time.
+  for (int p = 0; p < nbuf - 1; ++p) {
+    if (p * FORGET_CHUNK < n) issue(p, p * FORGET_CHUNK);
+    else asm volatile("cp.async.commit_group;\n" ::);
+  }
   float* S = state + ((size_t)slot * H + h) * d * dv;
   float s[ROWS];
 #pragma unroll
@@ -517,19 +523,60 @@ forget_scan_kernel(const float* __restrict__ qf, const float* __restrict__ v, fl
     s[r] = (on && row < d) ? S[(size_t)row * dv + col] : 0.f;
   }
   int which = 0;
-  for (int base = 0; base < n; base += FORGET_CHUNK, which ^= 1) {
+  for (int base = 0; base < n; base += FORGET_CHUNK, which = which + 1 == nbuf ? 0 : which + 1) {
     const int count = min(FORGET_CHUNK, n - base);
-    if (base + FORGET_CHUNK < n) {
-      issue(which ^ 1, base + FORGET_CHUNK);
-      asm volatile("cp.async.wait_group 1;\n" ::);
-    } else {
-      asm volatile("cp.async.wait_group 0;\n" ::);
-    }
+    const int ahead = base + (nbuf - 1) * FORGET_CHUNK;  // goes where the chunk before this one was
+    if (ahead < n) issue(which == 0 ? nbuf - 1 : which - 1, ahead);
+    else asm volatile("cp.async.commit_group;\n" ::);
+    if (nbuf == 4) asm volatile("cp.async.wait_group 3;\n" ::);
+    else asm volatile("cp.async.wait_group 1;\n" ::);
     __syncthreads();
     const float* buf = stage + which * buffer;
-    // (unrolled: a token's sum over lanes does not hold up the next token's update of the state)
-#pragma unroll 4
-    for (int i = 0; i < count; ++i) {
+    int i = 0;
+    if constexpr (VEC) {
+      // Several tokens at a time: a row's state goes through their updates in one chain of
+      // multiply-adds, the sums that read it are chains of their own, and their sums over lanes go
+      // side by side, so that a token's latencies are paid once per group of tokens.
+      const float* vbuf = buf + 2 * FORGET_CHUNK * d + min(col_local, cols - 1);
+      for (; i + FORGET_TOGETHER <= count; i += FORGET_TOGETHER) {
+        float od4[FORGET_TOGETHER], vv4[FORGET_TOGETHER];
+#pragma unroll
+        for (int t = 0; t < FORGET_TOGETHER; ++t) {
+          vv4[t] = vbuf[(i + t) * cols_pad];
+          od4[t] = 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS / 4; ++r) {
+          const int at = rs + RS * r;
+          if (4 * at < d) {
+#pragma unroll
+            for (int t = 0; t < FORGET_TOGETHER; ++t) {
+              const float4 f4 = reinterpret_cast<const float4*>(buf + (FORGET_CHUNK + i + t) * d)[at];
+              const float4 q4 = reinterpret_cast<const float4*>(buf + (i + t) * d)[at];
+              s[4 * r] = fmaf(f4.x, s[4 * r], (1.0f - f4.x) * vv4[t]);
+              s[4 * r + 1] = fmaf(f4.y, s[4 * r + 1], (1.0f - f4.y) * vv4[t]);
+              s[4 * r + 2] = fmaf(f4.z, s[4 * r + 2], (1.0f - f4.z) * vv4[t]);
+              s[4 * r + 3] = fmaf(f4.w, s[4 * r + 3], (1.0f - f4.w) * vv4[t]);
+              od4[t] = fmaf(s[4 * r], q4.x, od4[t]);
+              od4[t] = fmaf(s[4 * r + 1], q4.y, od4[t]);
+              od4[t] = fmaf(s[4 * r + 2], q4.z, od4[t]);
+              od4[t] = fmaf(s[4 * r + 3], q4.w, od4[t]);
+            }
+          }
+        }
+#pragma unroll
+        for (int o = 1; o < RS; o <<= 1) {
+#pragma unroll
+          for (int t = 0; t < FORGET_TOGETHER; ++t) od4[t] += __shfl_xor_sync(0xffffffffu, od4[t], o);
+        }
+        if (on && rs == 0) {
+          float* dst = out + ((size_t)(first + base + i) * H + h) * dv + col;
+#pragma unroll
+          for (int t = 0; t < FORGET_TOGETHER; ++t) dst[(size_t)t * H * dv] = od4[t];
+        }
+      }
+    }
+    for (; i < count; ++i) {
       const float* qq = buf + i * d;
       const float* ff = buf + (FORGET_CHUNK + i) * d;
       const float vv = buf[2 * FORGET_CHUNK * d + i * cols_pad + min(col_local, cols - 1)];
@@ -565,8 +612,9 @@ forget_scan_kernel(const float* __restrict__ qf, const float* __restrict__ v, fl
       for (int o = 1; o < RS; o <<= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
       if (on && rs == 0) out[((size_t)(first + base + i) * H + h) * dv + col] = od;
     }
-    __syncthreads();  // the buffer is filled again two chunks on
+    __syncthreads();  // the buffer is filled again in the next round
   }
+  asm volatile("cp.async.wait_group 0;\n" ::);
   if (on && first_row_of_slot(slots, b)) {
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
@@ -607,7 +655,9 @@ extern "C" int sb_forget_scan(const void* pre, int row_width, int dtype, const f
   if (cols > dv) cols = dv;
   const int block = ((cols * rs + 31) / 32) * 32;
   const dim3 grid(H, num_seqs, (dv + cols - 1) / cols);
-  const size_t smem = (size_t)2 * FORGET_CHUNK * (2 * d + ((cols + 3) & ~3)) * sizeof(float);
+  const size_t one = (size_t)FORGET_CHUNK * (2 * d + ((cols + 3) & ~3)) * sizeof(float);
+  const int nbuf = (max_q_len > 2 * FORGET_CHUNK && 4 * one <= 100 * 1024) ? 4 : 2;
+  const size_t smem = nbuf * one;
   if (smem > 200 * 1024) return -13;
 #define SB_FORGET_V(RS_, ROWS_, VEC_)                                                                          \
   do {                                                                                                         \
@@ -616,10 +666,10 @@ extern "C" int sb_forget_scan(const void* pre, int row_width, int dtype, const f
                            (int)smem);                                                                         \
     if (max_q_len >= 64)                                                                                       \
       sb_launch_plain(forget_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, (const float*)qf,       \
-                      (const float*)v, state, cu_q, slots, num_slots, H, d, dv, cols, out, err);               \
+                      (const float*)v, state, cu_q, slots, num_slots, H, d, dv, cols, nbuf, out, err);         \
     else                                                                                                       \
       sb_launch(forget_scan_kernel<RS_, ROWS_, VEC_>, grid, block, smem, stream, (const float*)qf,             \
-                (const float*)v, state, cu_q, slots, num_slots, H, d, dv, cols, out, err);                     \
+                (const float*)v, state, cu_q, slots, num_slots, H, d, dv, cols, nbuf, out, err);               \
   } while (0)
 #define SB_FORGET(RS_)                                \
   do {                                                \
