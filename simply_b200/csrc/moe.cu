@@ -497,3 +497,65 @@ extern "C" int sb_moe_combine(const void* x, const void* y_pair, int dtype, cons
   SB_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// The experts of a long prompt portion, one after the other through the dense products, issued
+// from here so that the host pays one call, not two per expert: rows [starts[i], starts[i] +
+// counts[i]) of xs (sorted by expert) go through expert experts[i]:
+//   h = act(xs W_gate^T) * (xs W_up^T)   the tcgen05 gated product (gemm_gated_tc.cu)
+//   y = h W_down^T                        the library's product (gemm_library.cu)
+// Returns -9 (nothing launched for that expert or any after it) when a product does not take the
+// shape; the caller then runs those experts through the kernel table's own methods.
+// One expert's products fill a part of the GPU only (32 tiles of 256 x 128 for 512 rows and 2,048
+// features, on 74 pairs of SMs): with `workspace2` every other expert goes to a second stream, which
+// starts after what `stream` holds so far and which `stream` waits for at the end.
+// ---------------------------------------------------------------------------
+extern "C" int sb_gemm_gated_tc(const void* x, const void* w, void* out, int M, int F, int K, int act, float limit,
+                                int blocks, int pairs, int* err, cudaStream_t stream);
+extern "C" int sb_gemm_library_bf16(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
+                                    void* workspace, long long workspace_bytes, cudaStream_t stream);
+
+extern "C" int sb_experts_dense_bf16(const void* xs, const void* gate_up, const void* down, void* h, void* y,
+                                     const int* starts, const int* counts, const int* experts, int num, int width,
+                                     int hidden, int act, int blocks, int pairs, void* workspace, void* workspace2,
+                                     long long workspace_bytes, int* done, int* err, cudaStream_t stream) {
+  *done = 0;
+  static cudaStream_t side = nullptr;
+  static cudaEvent_t fork_event = nullptr, join_event = nullptr;
+  bool two = workspace2 != nullptr && num > 1;
+  if (two && side == nullptr) {
+    if (cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&fork_event, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&join_event, cudaEventDisableTiming) != cudaSuccess) {
+      side = nullptr;
+      two = false;
+    }
+  }
+  if (two) {
+    cudaEventRecord(fork_event, stream);
+    cudaStreamWaitEvent(side, fork_event, 0);
+  }
+  // (whatever happens below, `stream` waits for the second stream before this returns)
+  struct Join {
+    bool on; cudaStream_t main, other; cudaEvent_t event;
+    ~Join() { if (on) { cudaEventRecord(event, other); cudaStreamWaitEvent(main, event, 0); } }
+  } join{two, stream, side, join_event};
+  cudaStream_t main_stream = stream;
+  void* main_workspace = workspace;
+  for (int i = 0; i < num; ++i) {
+    stream = (two && (i & 1)) ? side : main_stream;
+    workspace = (two && (i & 1)) ? workspace2 : main_workspace;
+    const size_t row = (size_t)starts[i];
+    const bf16* x_i = (const bf16*)xs + row * width;
+    bf16* h_i = (bf16*)h + row * hidden;
+    const bf16* gu = (const bf16*)gate_up + (size_t)experts[i] * 2 * hidden * width;
+    const bf16* dn = (const bf16*)down + (size_t)experts[i] * width * hidden;
+    int rc = sb_gemm_gated_tc(x_i, gu, h_i, counts[i], hidden, width, act, 0.f, blocks, pairs, err, stream);
+    if (rc != 0) return rc;
+    rc = sb_gemm_library_bf16(h_i, dn, (bf16*)y + row * width, counts[i], width, hidden, 0, workspace, workspace_bytes,
+                              stream);
+    if (rc != 0) return rc;  // (h_i is computed; the caller redoes this expert whole)
+    *done = i + 1;
+  }
+  return 0;
+}

@@ -182,6 +182,7 @@ class CudaOps:
     # at how many rows each got; below, and in decode graphs, the grouped kernel (csrc/moe.cu)
     # serves them without the host.  0: always the grouped kernel.
     self.expert_rows_for_dense_products = int(os.environ.get("SIMPLY_B200_EXPERT_DENSE_ROWS", "384"))
+    self.expert_side_stream = True  # False: all experts on the step's stream (tests, experiments)
     self._wide_tables: dict[tuple, torch.Tensor] = {}
     self.prefill_single_key_group = False  # True: 64-row tiles with 4 warps instead of 4 x 2 (experiments, tests)
     # 0: the weight-streaming product picks its warps per block; 4, 8 or 16 forces them (experiments).
@@ -288,6 +289,10 @@ class CudaOps:
       fn.restype = c_int
     self.lib.sb_gemm_library_bf16.argtypes = [c_void, c_void, c_void, c_int, c_int, c_int, c_int, c_void, c_ll, c_void]
     self.lib.sb_gemm_library_bf16.restype = c_int
+    c_ip = ctypes.POINTER(c_int)
+    self.lib.sb_experts_dense_bf16.argtypes = [c_void, c_void, c_void, c_void, c_void, c_ip, c_ip, c_ip, c_int, c_int,
+                                               c_int, c_int, c_int, c_int, c_void, c_void, c_ll, c_ip, c_void, c_void]
+    self.lib.sb_experts_dense_bf16.restype = c_int
     self.lib.sb_graph_burst.argtypes = [c_void, c_void, c_void, c_ll, c_int, c_void, c_void, c_ll, c_void]
     self.lib.sb_graph_burst.restype = c_int
     self.lib.sb_stream_wait.argtypes = [c_void]
@@ -995,19 +1000,49 @@ class CudaOps:
     """The experts' products of a long prompt portion: the rows, sorted by expert, are gathered once,
     the host reads how many each expert got (the one wait of the step), and every expert's rows go
     through the engine's own products for a dense feed-forward (the tcgen05 kernel with the
-    activation on its sums from 129 rows, the library's product for the way down).  Returns the rows
-    of every pair in sorted order, as the grouped kernel does."""
+    activation on its sums from 129 rows, the library's product for the way down), issued by one
+    native call that puts every other expert on a second stream (csrc/moe.cu).  Returns the rows of
+    every pair in sorted order, as the grouped kernel does."""
     expert, row0, count = tiles.cpu().numpy()
     total = int(count[expert >= 0].sum())  # (identity experts' pairs have no row; the list's tail is unused)
     rows_of = torch.div(sorted_pair[:total], top, rounding_mode="floor")
     xs = self.gather_rows(x, rows_of)
-    outs = []
-    for e in np.unique(expert[expert >= 0]):
-      mine = expert == e
-      start, n = int(row0[mine].min()), int(count[mine].sum())
-      h = self.gated_linear(xs[start:start + n], gate_up[e], activation)
-      outs.append(self.linear(h, down[e]))
-    return torch.cat(outs) if len(outs) != 1 else outs[0]
+    which = np.unique(expert[expert >= 0]).astype(np.int32)
+    starts = np.array([row0[expert == e].min() for e in which], dtype=np.int32)
+    counts = np.array([count[expert == e].sum() for e in which], dtype=np.int32)
+    width, hidden = x.shape[1], down.shape[2]
+    y = self._new(total, width, dtype=x.dtype)
+    # Experts with enough rows for the tcgen05 product: all of them in one call of the library, so
+    # that the host pays one call, not two per expert.  The others through the kernel table's methods.
+    big = counts >= self.gated_tc_min_rows if self.gated_tc_min_rows > 0 else np.zeros(len(counts), dtype=bool)
+    rest = [(int(e), int(s), int(n)) for e, s, n in zip(which[~big], starts[~big], counts[~big])]
+    which, starts, counts = (np.ascontiguousarray(a[big]) for a in (which, starts, counts))
+    if len(which):
+      stream = self._stream()
+      workspace = self._library_workspaces.get(stream.value)
+      if workspace is None:
+        workspace = self._library_workspaces[stream.value] = torch.empty(32 << 20, dtype=torch.uint8, device=self.device)
+      second = None
+      if self.expert_side_stream:  # every other expert on a second stream, with a workspace of its own
+        second = self._library_workspaces.get("experts")
+        if second is None:
+          second = self._library_workspaces["experts"] = torch.empty(32 << 20, dtype=torch.uint8, device=self.device)
+      h = self._new(total, hidden, dtype=x.dtype)
+      finished = ctypes.c_int(0)
+      as_ints = lambda a: a.ctypes.data_as(ctypes.POINTER(ctypes.c_int))
+      rc = self.lib.sb_experts_dense_bf16(
+          _ptr(xs), _ptr(gate_up), _ptr(down), _ptr(h), _ptr(y), as_ints(starts), as_ints(counts), as_ints(which),
+          len(which), width, hidden, activation, self.gated_tc_blocks, int(self.gated_tc_pairs), _ptr(workspace),
+          _ptr(second), workspace.numel(), ctypes.byref(finished), _ptr(self.err), stream)
+      if rc > 0:
+        raise KernelError(f"sb_experts_dense_bf16: CUDA or cuBLAS status {rc}")
+      done = finished.value
+      self.launches += 2 * done
+      rest += list(zip(which[done:].tolist(), starts[done:].tolist(), counts[done:].tolist()))
+    for e, start, n in rest:
+      h_e = self.gated_linear(xs[start:start + n], gate_up[e], activation)
+      y[start:start + n] = self.linear(h_e, down[e])
+    return y
 
   def mix_experts(self, x: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor, gate_up: torch.Tensor | None,
                   down: torch.Tensor | None, num_experts: int, activation: int, shared: torch.Tensor | None,
